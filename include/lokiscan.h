@@ -1,0 +1,208 @@
+/*
+ * lokiscan: B200-native exact vector scan behind the API of Lowkey Media Server's
+ * media-server/embedindex + media-server/embedvec packages.
+ *
+ * The reference is pure Go with no FFI, so this header is the boundary a cgo
+ * binding would call.  Strings never cross it: the caller keeps the path <-> slot
+ * map (media-server/embedindex/embedindex.go:122-126) and this library sees slot
+ * numbers only.  Every function returns an lk_status (0 = success) unless noted;
+ * lk_last_error() gives the message for the calling thread's last failure.
+ *
+ * Threading contract (same as media-server/embedindex/embedindex.go:90-92): calls
+ * on one handle must be serialised by the caller; distinct handles may be used
+ * concurrently.  All pointers are host pointers borrowed for the duration of the
+ * call unless a parameter is documented as a device pointer.
+ *
+ * There is no CPU fallback: every entry point that computes needs a CUDA device
+ * and fails with LK_ECUDA without one.
+ */
+#ifndef LOKISCAN_H
+#define LOKISCAN_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LK_API __attribute__((visibility("default")))
+
+typedef enum {
+    LK_OK = 0,
+    LK_EINVAL = 1,   /* bad argument */
+    LK_EDIM = 2,     /* vector length does not match the index */
+    LK_ENOMEM = 3,   /* host or device allocation failed */
+    LK_ECUDA = 4,    /* CUDA runtime error (message in lk_last_error) */
+    LK_ENCCL = 5,    /* NCCL error or NCCL not loadable */
+    LK_ETIMEOUT = 6, /* a bounded device-side or host-side wait ran out */
+    LK_ERANGE = 7    /* size beyond a documented limit */
+} lk_status;
+
+/* Storage type of the corpus rows (what the scan streams from HBM). */
+typedef enum {
+    LK_F32 = 0, /* L2-normalised float32: the reference's own representation */
+    LK_F16 = 1, /* L2-normalised, rounded to IEEE half */
+    LK_I8 = 2   /* L2-normalised, per-row symmetric int8 codes + float32 scale */
+} lk_dtype;
+
+/* Scoring mode of a query: media-server/embedindex/embedindex.go:64-77. */
+typedef enum {
+    LK_SCORE_DEFAULT = 0, /* centered cosine on a centered index, else plain */
+    LK_SCORE_PLAIN = 1    /* always plain cosine (cross-modal queries) */
+} lk_scoring;
+
+#define LK_MIN_CENTER_COUNT 64 /* media-server/embedindex/embedindex.go:55 */
+#define LK_MAX_DIM 8192
+#define LK_SHARED_MAX_TERMS 32 /* positives + basis + negatives of one shared query */
+
+typedef struct lk_index lk_index;
+typedef struct lk_queries lk_queries;
+typedef struct lk_comm lk_comm;
+
+/* ---- library ------------------------------------------------------------ */
+
+/* Message of the calling thread's most recent failed call ("" if none). */
+LK_API const char *lk_last_error(void);
+/* Number of CUDA devices visible (0 when there is no driver or no GPU). */
+LK_API int lk_device_count(void);
+/* Library version, e.g. "0.1.0". */
+LK_API const char *lk_version(void);
+
+/* ---- index life cycle --------------------------------------------------- */
+
+/* Replaces embedindex.New() / NewCentered() (media-server/embedindex/embedindex.go:144-153).
+ * dim: vector length (1..LK_MAX_DIM).  store: lk_dtype.  centered != 0 enables
+ * mean-centering (float32 storage only).  device: CUDA ordinal. */
+LK_API int lk_index_create(int dim, int store, int centered, int device, lk_index **out);
+LK_API int lk_index_destroy(lk_index *idx);
+/* Pre-size device storage for n rows (growth is otherwise geometric). */
+LK_API int lk_index_reserve(lk_index *idx, int64_t n);
+/* Replaces Len() (media-server/embedindex/embedindex.go:219). */
+LK_API int64_t lk_index_len(const lk_index *idx);
+LK_API int lk_index_dim(const lk_index *idx);
+
+/* Replaces Add (media-server/embedindex/embedindex.go:176-194) for n rows at once:
+ * rows[i] (dim floats each, raw model output) is L2-normalised on the device
+ * (float64 sum of squares in index order, like embedvec.Normalize,
+ * media-server/embedvec/embedvec.go:34-50), converted to the storage type and
+ * written to slot first_slot+i.  first_slot <= len; slots below len are
+ * overwritten in place, slots from len on are appended.  A centered index keeps
+ * its float64 column sum and, once centering is live, its per-row centered norm
+ * up to date exactly as Add does. */
+LK_API int lk_index_upsert_f32(lk_index *idx, int64_t first_slot, int64_t n, const float *rows);
+/* Same, rows being a DEVICE pointer on the index's device (row stride = dim). */
+LK_API int lk_index_upsert_f32_device(lk_index *idx, int64_t first_slot, int64_t n,
+                                      const float *d_rows);
+/* Replaces the storage half of Delete (media-server/embedindex/embedindex.go:196-217):
+ * the last row moves into `slot` and the length drops by one.  The caller
+ * mirrors the move in its own path table. */
+LK_API int lk_index_swap_remove(lk_index *idx, int64_t slot);
+
+/* Read back stored rows [first, first+n): `out` receives n*dim elements of the
+ * storage type (float, uint16 half bits or int8), padding stripped; `scales`
+ * (may be NULL) receives the n int8 scales.  For tests and for callers that
+ * need a stored vector (Delete's column-sum bookkeeping is done internally). */
+LK_API int lk_index_read_rows(lk_index *idx, int64_t first, int64_t n, void *out, float *scales);
+
+/* Centering state (media-server/embedindex/embedindex.go:127-139): *live is 1 when a
+ * mean is in use; mu (dim floats), sum (dim doubles), cnorm (len floats) may
+ * each be NULL.  Does not trigger a re-centre. */
+LK_API int lk_index_center_state(lk_index *idx, int *live, int64_t *n_centered, double *mu_n2,
+                                 float *mu, double *sum, float *cnorm);
+
+/* ---- search ------------------------------------------------------------- */
+
+/* Replaces Search / SearchFiltered / SearchScored
+ * (media-server/embedindex/embedindex.go:308-328) for nq independent queries.
+ *   queries      nq*dim floats, raw (normalised internally, like the reference)
+ *   k            hits wanted per query; k' = min(k, candidates) are returned
+ *   scoring      lk_scoring
+ *   allow_slots  NULL = every row; else n_allow DISTINCT slot numbers to score
+ *                (the resolved allow set, media-server/embedindex/embedindex.go:398-419);
+ *                n_allow == 0 returns no hits
+ *   out_ids      nq*k slot numbers (plus the shard base when one is set), rank order
+ *   out_scores   nq*k float scores (cosine; for LK_I8 the de-quantised dot
+ *                int_score * scale_query * scale_row)
+ *   out_iscores  NULL or nq*k raw int32 dots (LK_I8 only; zero otherwise)
+ *   out_counts   nq hit counts
+ * Rank order is score descending, slot ascending on equal scores (for LK_I8 the
+ * key is the raw int32 dot).  A centered index re-centres first when it has
+ * drifted (media-server/embedindex/embedindex.go:234-268), so this call may mutate.
+ * With a communicator attached (lk_index_attach_comm) every rank must call with
+ * the same queries and k and receives the merged global result. */
+LK_API int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring,
+                     const int32_t *allow_slots, int64_t n_allow,
+                     int64_t *out_ids, float *out_scores, int32_t *out_iscores,
+                     int32_t *out_counts);
+
+/* Replaces SearchShared / SearchSharedScored
+ * (media-server/embedindex/embedindex.go:334-394, media-server/embedvec/shared.go:61-220).
+ * pos: npos*dim floats, posw: NULL (equal) or npos weights > 0; neg/negw: nneg
+ * steer-away terms.  beta/lambda as embedvec.NewSharedQuery (defaults 0.25 / 1.0).
+ * float32 storage only.  LK_EINVAL mirrors the reference's constructor errors. */
+LK_API int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npos,
+                            const float *neg, const float *negw, int nneg,
+                            float beta, float lambda, int k, int scoring,
+                            const int32_t *allow_slots, int64_t n_allow,
+                            int64_t *out_ids, float *out_scores, int32_t *out_count);
+
+/* ---- device-resident queries (throughput measurement, pipelined callers) -- */
+
+/* Prepare nq queries (normalise, centre/quantise as the index requires) and keep
+ * them on the device. */
+LK_API int lk_queries_create(lk_index *idx, const float *queries, int nq, int scoring,
+                             lk_queries **out);
+LK_API int lk_queries_destroy(lk_queries *q);
+/* Enqueue one scan per query [first, first+count) on the index's stream, no host
+ * synchronisation; results stay on the device until lk_queries_fetch. */
+LK_API int lk_search_resident(lk_index *idx, lk_queries *q, int first, int count, int k);
+/* Wait for the stream and copy the results of queries [first, first+count) out. */
+LK_API int lk_queries_fetch(lk_index *idx, lk_queries *q, int first, int count, int k,
+                            int64_t *out_ids, float *out_scores, int32_t *out_iscores,
+                            int32_t *out_counts);
+/* CUDA-event stopwatch on the index's stream. */
+LK_API int lk_timer_start(lk_index *idx);
+LK_API int lk_timer_stop(lk_index *idx, float *elapsed_ms);
+LK_API int lk_index_sync(lk_index *idx);
+
+/* ---- multi-GPU: row shards + one all-gather of candidates ---------------- */
+
+/* 128-byte NCCL unique id, created on one rank and passed to the others by the caller. */
+LK_API int lk_comm_unique_id(void *out128);
+LK_API int lk_comm_create(int world, int rank, int device, const void *id128, lk_comm **out);
+LK_API int lk_comm_destroy(lk_comm *c);
+/* This index holds global rows [shard_base, shard_base+len). */
+LK_API int lk_index_attach_comm(lk_index *idx, lk_comm *c, int64_t shard_base);
+LK_API int lk_index_set_shard_base(lk_index *idx, int64_t shard_base);
+
+/* ---- 64-bit Hamming (no counterpart in the reference) --------------------- */
+
+/* All pairs i<j of hashes[0..n) with popcount(a^b) <= radius, written to `pairs`
+ * as (i,j) uint32 couples in lexicographic order, at most cap couples;
+ * *count = total found (may exceed cap).  part/parts split the upper triangle
+ * across callers (0/1 = everything). */
+LK_API int lk_hamming_pairs(const uint64_t *hashes, int64_t n, int radius, int part, int parts,
+                            int device, uint32_t *pairs, int64_t cap, int64_t *count);
+/* One hash against n: ids (ascending) and distances of those within radius. */
+LK_API int lk_hamming_scan(const uint64_t *hashes, int64_t n, uint64_t query, int radius,
+                           int device, uint32_t *out_ids, int32_t *out_dist, int64_t cap,
+                           int64_t *count);
+
+/* ---- statistics ----------------------------------------------------------- */
+
+typedef struct {
+    int64_t len;
+    int64_t capacity;
+    int64_t bytes_resident;    /* device bytes held by this index */
+    int64_t scan_launches;     /* scan kernels launched so far */
+    int64_t aux_launches;      /* other kernels launched so far */
+    float last_search_ms;      /* wall time of the last lk_search call */
+    int grid;                  /* CTAs per scan launch */
+    int sm_count;
+} lk_stats_t;
+LK_API int lk_stats(lk_index *idx, lk_stats_t *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOKISCAN_H */

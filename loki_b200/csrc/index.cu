@@ -1,0 +1,686 @@
+// C-ABI of the library (include/lokiscan.h): index storage in HBM, query
+// preparation on the host, kernel launches, result marshalling.
+//
+// HBM layout of one index (all cudaMalloc'd, 256-byte aligned):
+//   rows    capacity x ld bytes, row-major, ld = row bytes rounded up to 16 so
+//           that every row starts on a 16-byte boundary (padding is zero)
+//   scales  capacity x float   (int8 storage: per-row scale)
+//   cnorm   capacity x float   (centered index: |row - mean|)
+//   sum     dim x double, mu dim x float (centered index)
+//   part    grid x k ranking keys + one ticket word: scratch of the scan kernel
+//   result arena, query buffer, slot list, upload staging: grown on demand
+#include <algorithm>
+#include <chrono>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/lokiscan.h"
+#include "build.cuh"
+#include "comm.hpp"
+#include "hostmath.hpp"
+#include "index_internal.cuh"
+#include "lk_common.cuh"
+#include "scan.cuh"
+#include "shared.cuh"
+#include "topk.cuh"
+
+namespace lk {
+
+static thread_local std::string g_err;
+void set_error(const std::string &msg) { g_err = msg; }
+int fail(int status, const std::string &msg) {
+    g_err = msg;
+    return status;
+}
+
+}  // namespace lk
+
+using namespace lk;
+
+namespace lk {
+
+static int use_device(const lk_index *idx) {
+    LK_CUDA(cudaSetDevice(idx->device));
+    return 0;
+}
+
+static int elem_bytes(int store) { return store == LK_F32 ? 4 : (store == LK_F16 ? 2 : 1); }
+
+static int grow_rows(lk_index *idx, long long need) {
+    if (need <= idx->cap) return 0;
+    long long ncap = std::max<long long>(need, std::max<long long>(idx->cap * 2, 1024));
+    unsigned char *nrows = nullptr;
+    float *nscales = nullptr, *ncnorm = nullptr;
+    cudaError_t e = cudaMalloc((void **)&nrows, (size_t)ncap * idx->ld);
+    if (e == cudaSuccess && idx->store == LK_I8) e = cudaMalloc((void **)&nscales, (size_t)ncap * 4);
+    if (e == cudaSuccess && idx->centered) e = cudaMalloc((void **)&ncnorm, (size_t)ncap * 4);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (nrows) cudaFree(nrows);
+        if (nscales) cudaFree(nscales);
+        if (ncnorm) cudaFree(ncnorm);
+        return fail(LK_ENOMEM, std::string("growing the index to ") + std::to_string(ncap) + " rows: " + cudaGetErrorString(e));
+    }
+    if (idx->len > 0) {
+        LK_CUDA(cudaMemcpyAsync(nrows, idx->d_rows, (size_t)idx->len * idx->ld, cudaMemcpyDeviceToDevice, idx->stream));
+        if (nscales) LK_CUDA(cudaMemcpyAsync(nscales, idx->d_scales, (size_t)idx->len * 4, cudaMemcpyDeviceToDevice, idx->stream));
+        if (ncnorm && idx->d_cnorm) LK_CUDA(cudaMemcpyAsync(ncnorm, idx->d_cnorm, (size_t)idx->len * 4, cudaMemcpyDeviceToDevice, idx->stream));
+        LK_CUDA(cudaStreamSynchronize(idx->stream));
+    }
+    if (idx->d_rows) cudaFree(idx->d_rows);
+    if (idx->d_scales) cudaFree(idx->d_scales);
+    if (idx->d_cnorm) cudaFree(idx->d_cnorm);
+    idx->d_rows = nrows;
+    idx->d_scales = nscales;
+    idx->d_cnorm = ncnorm;
+    idx->cap = ncap;
+    return 0;
+}
+
+// Add for n rows already on the device (media-server/embedindex/embedindex.go:176-194).
+static int upsert_device(lk_index *idx, long long first, long long n, const float *d_src) {
+    if (n == 0) return 0;
+    LK_TRY(grow_rows(idx, first + n));
+    const long long n_over = std::max<long long>(0, std::min(n, idx->len - first));
+    unsigned char *dst = idx->d_rows + (size_t)first * idx->ld;
+    if (idx->centered && n_over > 0) {
+        LK_TRY(colsum_update_launch(dst, idx->ld, n_over, idx->dim, idx->d_sum, -1, idx->stream));
+        idx->aux_launches++;
+    }
+    LK_TRY(normalize_store_launch(idx->store, d_src, n, idx->dim, dst, idx->ld,
+                                  idx->d_scales ? idx->d_scales + first : nullptr, idx->sm_count, idx->stream));
+    idx->aux_launches++;
+    if (idx->centered) {
+        LK_TRY(colsum_update_launch(dst, idx->ld, n, idx->dim, idx->d_sum, +1, idx->stream));
+        idx->aux_launches++;
+    }
+    idx->len = std::max(idx->len, first + n);
+    if (idx->center_live) {
+        LK_TRY(centered_norm_launch(idx->d_rows, idx->ld, first, n, idx->dim, idx->d_mu, idx->mu_n2,
+                                    idx->d_cnorm, idx->sm_count, idx->stream));
+        idx->aux_launches++;
+    }
+    return 0;
+}
+
+// media-server/embedindex/embedindex.go:234-268
+static int maybe_recenter(lk_index *idx) {
+    if (!idx->centered) return 0;
+    const long long n = idx->len;
+    if (n < LK_MIN_CENTER_COUNT) {
+        idx->center_live = false;
+        idx->n_centered = n;
+        return 0;
+    }
+    if (idx->center_live) {
+        long long drift = n - idx->n_centered;
+        if (drift < 0) drift = -drift;
+        if (drift <= idx->n_centered / 10 + 32) return 0;
+    }
+    std::vector<double> sum((size_t)idx->dim);
+    LK_CUDA(cudaMemcpyAsync(sum.data(), idx->d_sum, sizeof(double) * idx->dim, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    idx->h_mu.assign((size_t)idx->dim, 0.0f);
+    idx->mu_n2 = hm::mean_from_sum(sum.data(), idx->dim, n, idx->h_mu.data());
+    LK_CUDA(cudaMemcpyAsync(idx->d_mu, idx->h_mu.data(), sizeof(float) * idx->dim, cudaMemcpyHostToDevice, idx->stream));
+    LK_TRY(centered_norm_launch(idx->d_rows, idx->ld, 0, n, idx->dim, idx->d_mu, idx->mu_n2, idx->d_cnorm,
+                                idx->sm_count, idx->stream));
+    idx->aux_launches++;
+    LK_CUDA(cudaStreamSynchronize(idx->stream));  // h_mu is pageable: finish the copy before it can change
+    idx->center_live = true;
+    idx->n_centered = n;
+    return 0;
+}
+
+// Normalise one raw query and convert it to what the scan kernel reads.
+// Returns whether the query is scored centered.
+static bool prepare_query(const lk_index *idx, const float *q, int scoring, unsigned char *dst,
+                          float *cq, float *qscale) {
+    const int d = idx->dim;
+    std::vector<float> qn((size_t)d);
+    hm::normalize(q, d, qn.data());
+    memset(dst, 0, (size_t)idx->qbytes);
+    *cq = 0.0f;
+    *qscale = 0.0f;
+    if (idx->store == LK_I8) {
+        *qscale = hm::quantize_i8(qn.data(), d, reinterpret_cast<int8_t *>(dst));
+        return false;
+    }
+    float *out = reinterpret_cast<float *>(dst);
+    if (idx->store == LK_F32 && idx->center_live && scoring != LK_SCORE_PLAIN) {
+        *cq = hm::center_query(qn.data(), idx->h_mu.data(), d, out);
+        return true;
+    }
+    memcpy(out, qn.data(), sizeof(float) * (size_t)d);
+    return false;
+}
+
+static int ensure_scan_scratch(lk_index *idx, int k) {
+    if (idx->grid_for_k != k) {
+        int err = 0;
+        const int g = scan_resident_grid(idx->type, idx->chunks, k, idx->device, &err);
+        if (err != 0 || g <= 0)
+            return fail(LK_ECUDA, std::string("scan occupancy query: ") + cudaGetErrorString((cudaError_t)err));
+        idx->grid = g;
+        idx->grid_for_k = k;
+    }
+    LK_TRY(idx->part.reserve((size_t)idx->grid * k * 8));
+    return 0;
+}
+
+// Enqueue the scan(s) of one prepared query.  k_eff hits are selected in passes of
+// at most kMaxK; pass p accepts only keys below the last key of pass p-1.
+static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered, float cq, float qscale,
+                         const int *d_slots, long long n_cand, int k_eff, int k_stride, int passes,
+                         const ResultArena &res, int qi) {
+    for (int p = 0; p < passes; ++p) {
+        const int done = p * kMaxK;
+        const int kk = std::min(kMaxK, k_eff - done);
+        ScanArgs a;
+        a.rows = idx->d_rows;
+        a.ld = idx->ld;
+        a.chunks = idx->chunks;
+        a.n = n_cand;
+        a.slots = d_slots;
+        a.query = d_q;
+        a.cnorm = centered ? idx->d_cnorm : nullptr;
+        a.cq = cq;
+        a.k = kk;
+        const size_t o = (size_t)qi * k_stride + done;
+        a.bound = (p == 0) ? nullptr : res.d_keys() + o - 1;
+        a.part = (unsigned long long *)idx->part.p;
+        a.ticket = idx->d_ticket;
+        a.out_keys = res.d_keys() + o;
+        a.out_ids = res.d_ids() + o;
+        a.out_scores = res.d_scores() + o;
+        a.out_iscores = res.d_iscores() + o;
+        a.out_count = res.d_counts() + (size_t)qi * passes + p;
+        a.scales = idx->d_scales;
+        a.qscale = qscale;
+        a.shard_base = idx->shard_base;
+        LK_TRY(scan_launch(idx->type, a, idx->grid, idx->stream));
+        idx->scan_launches++;
+    }
+    return 0;
+}
+
+static void unpack_results(const ResultArena &res, int nq, int k_user, int k_eff, int passes,
+                           int64_t *out_ids, float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+    for (int q = 0; q < nq; ++q) {
+        int cnt = 0;
+        for (int p = 0; p < passes; ++p) cnt += res.h_counts()[(size_t)q * passes + p];
+        if (cnt > k_eff) cnt = k_eff;
+        const size_t so = (size_t)q * res.k, uo = (size_t)q * k_user;
+        for (int i = 0; i < k_user; ++i) {
+            const bool hit = i < cnt;
+            if (out_ids) out_ids[uo + i] = hit ? (int64_t)res.h_ids()[so + i] : -1;
+            if (out_scores) out_scores[uo + i] = hit ? res.h_scores()[so + i] : 0.0f;
+            if (out_iscores) out_iscores[uo + i] = hit ? res.h_iscores()[so + i] : 0;
+        }
+        if (out_counts) out_counts[q] = cnt;
+    }
+}
+
+}  // namespace lk
+
+// ===========================================================================
+// C ABI
+// ===========================================================================
+extern "C" {
+
+const char *lk_last_error(void) { return g_err.c_str(); }
+
+const char *lk_version(void) { return "0.1.0"; }
+
+int lk_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int lk_index_create(int dim, int store, int centered, int device, lk_index **out) {
+    if (!out) return fail(LK_EINVAL, "lk_index_create: out is NULL");
+    *out = nullptr;
+    if (dim < 1 || dim > LK_MAX_DIM) return fail(LK_EDIM, "lk_index_create: dim out of range");
+    if (store != LK_F32 && store != LK_F16 && store != LK_I8) return fail(LK_EINVAL, "lk_index_create: unknown storage type");
+    if (centered && store != LK_F32) return fail(LK_EINVAL, "lk_index_create: centering needs float32 storage");
+    if (lk_device_count() <= device || device < 0)
+        return fail(LK_ECUDA, "lk_index_create: no such CUDA device (this library has no CPU path)");
+    LK_CUDA(cudaSetDevice(device));
+    lk_index *idx = new (std::nothrow) lk_index();
+    if (!idx) return fail(LK_ENOMEM, "lk_index_create: out of host memory");
+    idx->dim = dim;
+    idx->store = store;
+    idx->centered = centered ? 1 : 0;
+    idx->device = device;
+    idx->type = store == LK_F32 ? SCAN_F32 : (store == LK_F16 ? SCAN_F16 : SCAN_I8);
+    idx->ld = round_up((int64_t)dim * elem_bytes(store), 16);
+    idx->chunks = (int)(idx->ld / 16);
+    idx->qbytes = scan_query_bytes(idx->type, idx->ld);
+    int st = 0;
+    do {
+        cudaError_t e = cudaStreamCreateWithFlags(&idx->stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreate(&idx->ev0);
+        if (e == cudaSuccess) e = cudaEventCreate(&idx->ev1);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&idx->sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (e == cudaSuccess) e = cudaMalloc((void **)&idx->d_ticket, 256);
+        if (e == cudaSuccess) e = cudaMemsetAsync(idx->d_ticket, 0, 256, idx->stream);
+        if (e == cudaSuccess && centered) {
+            e = cudaMalloc((void **)&idx->d_sum, sizeof(double) * dim);
+            if (e == cudaSuccess) e = cudaMemsetAsync(idx->d_sum, 0, sizeof(double) * dim, idx->stream);
+            if (e == cudaSuccess) e = cudaMalloc((void **)&idx->d_mu, (size_t)idx->ld);
+            if (e == cudaSuccess) e = cudaMemsetAsync(idx->d_mu, 0, (size_t)idx->ld, idx->stream);
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(idx->stream);
+        if (e != cudaSuccess) st = fail(LK_ECUDA, std::string("lk_index_create: ") + cudaGetErrorString(e));
+    } while (0);
+    if (st != 0) {
+        lk_index_destroy(idx);
+        return st;
+    }
+    *out = idx;
+    return LK_OK;
+}
+
+int lk_index_destroy(lk_index *idx) {
+    if (!idx) return LK_OK;
+    cudaSetDevice(idx->device);
+    if (idx->stream) cudaStreamSynchronize(idx->stream);
+    if (idx->d_rows) cudaFree(idx->d_rows);
+    if (idx->d_scales) cudaFree(idx->d_scales);
+    if (idx->d_cnorm) cudaFree(idx->d_cnorm);
+    if (idx->d_sum) cudaFree(idx->d_sum);
+    if (idx->d_mu) cudaFree(idx->d_mu);
+    if (idx->d_ticket) cudaFree(idx->d_ticket);
+    idx->part.release();
+    idx->res.release();
+    idx->d_query.release();
+    idx->d_slots.release();
+    idx->d_stage.release();
+    idx->h_query.release();
+    idx->gather.release();
+    if (idx->ev0) cudaEventDestroy(idx->ev0);
+    if (idx->ev1) cudaEventDestroy(idx->ev1);
+    if (idx->stream) cudaStreamDestroy(idx->stream);
+    cudaGetLastError();
+    delete idx;
+    return LK_OK;
+}
+
+int lk_index_reserve(lk_index *idx, int64_t n) {
+    if (!idx || n < 0) return fail(LK_EINVAL, "lk_index_reserve: bad argument");
+    LK_TRY(use_device(idx));
+    return grow_rows(idx, n);
+}
+
+int64_t lk_index_len(const lk_index *idx) { return idx ? idx->len : 0; }
+int lk_index_dim(const lk_index *idx) { return idx ? idx->dim : 0; }
+
+int lk_index_upsert_f32_device(lk_index *idx, int64_t first_slot, int64_t n, const float *d_rows) {
+    if (!idx || n < 0 || (n > 0 && !d_rows)) return fail(LK_EINVAL, "lk_index_upsert_f32_device: bad argument");
+    if (first_slot < 0 || first_slot > idx->len) return fail(LK_EINVAL, "lk_index_upsert: first_slot must be within [0, len]");
+    if (first_slot + n > 0xfffffff0ll) return fail(LK_ERANGE, "lk_index_upsert: more than 2^32-16 rows");
+    LK_TRY(use_device(idx));
+    LK_TRY(upsert_device(idx, first_slot, n, d_rows));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    return LK_OK;
+}
+
+int lk_index_upsert_f32(lk_index *idx, int64_t first_slot, int64_t n, const float *rows) {
+    if (!idx || n < 0 || (n > 0 && !rows)) return fail(LK_EINVAL, "lk_index_upsert_f32: bad argument");
+    if (first_slot < 0 || first_slot > idx->len) return fail(LK_EINVAL, "lk_index_upsert: first_slot must be within [0, len]");
+    if (first_slot + n > 0xfffffff0ll) return fail(LK_ERANGE, "lk_index_upsert: more than 2^32-16 rows");
+    LK_TRY(use_device(idx));
+    LK_TRY(grow_rows(idx, first_slot + n));
+    const size_t row_bytes = sizeof(float) * (size_t)idx->dim;
+    const long long chunk_rows = std::max<long long>(1, (long long)((64u << 20) / row_bytes));
+    LK_TRY(idx->d_stage.reserve((size_t)std::min<long long>(n, chunk_rows) * row_bytes));
+    for (long long off = 0; off < n; off += chunk_rows) {
+        const long long m = std::min(chunk_rows, n - off);
+        LK_CUDA(cudaMemcpyAsync(idx->d_stage.p, rows + (size_t)off * idx->dim, (size_t)m * row_bytes,
+                                cudaMemcpyHostToDevice, idx->stream));
+        LK_TRY(upsert_device(idx, first_slot + off, m, (const float *)idx->d_stage.p));
+        LK_CUDA(cudaStreamSynchronize(idx->stream));
+    }
+    return LK_OK;
+}
+
+int lk_index_swap_remove(lk_index *idx, int64_t slot) {
+    if (!idx) return fail(LK_EINVAL, "lk_index_swap_remove: idx is NULL");
+    if (slot < 0 || slot >= idx->len) return fail(LK_EINVAL, "lk_index_swap_remove: slot out of range");
+    LK_TRY(use_device(idx));
+    unsigned char *hole = idx->d_rows + (size_t)slot * idx->ld;
+    if (idx->centered) {
+        LK_TRY(colsum_update_launch(hole, idx->ld, 1, idx->dim, idx->d_sum, -1, idx->stream));
+        idx->aux_launches++;
+    }
+    const long long last = idx->len - 1;
+    if (slot != last) {
+        LK_CUDA(cudaMemcpyAsync(hole, idx->d_rows + (size_t)last * idx->ld, (size_t)idx->ld, cudaMemcpyDeviceToDevice, idx->stream));
+        if (idx->d_scales) LK_CUDA(cudaMemcpyAsync(idx->d_scales + slot, idx->d_scales + last, 4, cudaMemcpyDeviceToDevice, idx->stream));
+        if (idx->d_cnorm && idx->center_live) LK_CUDA(cudaMemcpyAsync(idx->d_cnorm + slot, idx->d_cnorm + last, 4, cudaMemcpyDeviceToDevice, idx->stream));
+    }
+    idx->len = last;
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    return LK_OK;
+}
+
+int lk_index_read_rows(lk_index *idx, int64_t first, int64_t n, void *out, float *scales) {
+    if (!idx || first < 0 || n < 0 || first + n > idx->len || (n > 0 && !out)) return fail(LK_EINVAL, "lk_index_read_rows: bad range");
+    if (n == 0) return LK_OK;
+    LK_TRY(use_device(idx));
+    const size_t rb = (size_t)idx->dim * elem_bytes(idx->store);
+    LK_CUDA(cudaMemcpy2DAsync(out, rb, idx->d_rows + (size_t)first * idx->ld, (size_t)idx->ld, rb, (size_t)n,
+                              cudaMemcpyDeviceToHost, idx->stream));
+    if (scales && idx->d_scales)
+        LK_CUDA(cudaMemcpyAsync(scales, idx->d_scales + first, (size_t)n * 4, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    return LK_OK;
+}
+
+int lk_index_center_state(lk_index *idx, int *live, int64_t *n_centered, double *mu_n2, float *mu, double *sum, float *cnorm) {
+    if (!idx) return fail(LK_EINVAL, "lk_index_center_state: idx is NULL");
+    LK_TRY(use_device(idx));
+    if (live) *live = idx->center_live ? 1 : 0;
+    if (n_centered) *n_centered = idx->n_centered;
+    if (mu_n2) *mu_n2 = idx->mu_n2;
+    if (mu && idx->center_live) memcpy(mu, idx->h_mu.data(), sizeof(float) * (size_t)idx->dim);
+    if (sum && idx->d_sum) LK_CUDA(cudaMemcpyAsync(sum, idx->d_sum, sizeof(double) * idx->dim, cudaMemcpyDeviceToHost, idx->stream));
+    if (cnorm && idx->center_live && idx->len > 0)
+        LK_CUDA(cudaMemcpyAsync(cnorm, idx->d_cnorm, sizeof(float) * (size_t)idx->len, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    return LK_OK;
+}
+
+int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, const int32_t *allow_slots,
+              int64_t n_allow, int64_t *out_ids, float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+    if (!idx || nq < 0 || (nq > 0 && !queries)) return fail(LK_EINVAL, "lk_search: bad argument");
+    if (allow_slots == nullptr && n_allow > 0) return fail(LK_EINVAL, "lk_search: n_allow without allow_slots");
+    const auto t0 = std::chrono::steady_clock::now();
+    LK_TRY(use_device(idx));
+    LK_TRY(maybe_recenter(idx));
+    const bool filtered = allow_slots != nullptr;
+    const long long n_cand = filtered ? (long long)n_allow : idx->len;
+    if (filtered)
+        for (int64_t i = 0; i < n_allow; ++i)
+            if (allow_slots[i] < 0 || allow_slots[i] >= idx->len) return fail(LK_EINVAL, "lk_search: allow slot out of range");
+    auto no_hits = [&]() {
+        for (int q = 0; q < nq; ++q) {
+            if (out_counts) out_counts[q] = 0;
+            for (int i = 0; i < std::max(k, 0); ++i) {
+                if (out_ids) out_ids[(size_t)q * k + i] = -1;
+                if (out_scores) out_scores[(size_t)q * k + i] = 0.0f;
+                if (out_iscores) out_iscores[(size_t)q * k + i] = 0;
+            }
+        }
+        return (int)LK_OK;
+    };
+    const bool sharded = idx->comm != nullptr;
+    if (nq == 0 || k <= 0) return no_hits();
+    if (n_cand == 0 && !sharded) return no_hits();
+    // Per-shard k: a shard can contribute at most min(k, its candidates) hits, but with a
+    // communicator every rank must run the same k so that the gathered lists line up.
+    const int k_eff = sharded ? k : (int)std::min<long long>(k, n_cand);
+    const int passes = (k_eff + kMaxK - 1) / kMaxK;
+    if (sharded && passes > 1) return fail(LK_ERANGE, "lk_search: k above the single-pass limit is not supported on a sharded index");
+    LK_TRY(ensure_scan_scratch(idx, std::min(k_eff, kMaxK)));
+    LK_TRY(idx->res.shape(nq, k_eff, passes));
+
+    // queries: prepare on the host, one upload
+    LK_TRY(idx->h_query.reserve((size_t)nq * idx->qbytes));
+    LK_TRY(idx->d_query.reserve((size_t)nq * idx->qbytes));
+    std::vector<float> cq((size_t)nq), qscale((size_t)nq);
+    std::vector<char> cen((size_t)nq);
+    for (int q = 0; q < nq; ++q)
+        cen[q] = prepare_query(idx, queries + (size_t)q * idx->dim, scoring,
+                               (unsigned char *)idx->h_query.p + (size_t)q * idx->qbytes, &cq[q], &qscale[q]);
+    LK_CUDA(cudaMemcpyAsync(idx->d_query.p, idx->h_query.p, (size_t)nq * idx->qbytes, cudaMemcpyHostToDevice, idx->stream));
+    const int *d_slots = nullptr;
+    if (filtered && n_cand > 0) {
+        LK_TRY(idx->d_slots.reserve((size_t)n_cand * 4));
+        LK_CUDA(cudaMemcpyAsync(idx->d_slots.p, allow_slots, (size_t)n_cand * 4, cudaMemcpyHostToDevice, idx->stream));
+        d_slots = (const int *)idx->d_slots.p;
+    }
+    for (int q = 0; q < nq; ++q)
+        LK_TRY(enqueue_query(idx, (const unsigned char *)idx->d_query.p + (size_t)q * idx->qbytes, cen[q] != 0, cq[q],
+                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q));
+    if (sharded) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
+    LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    unpack_results(idx->res, nq, k, k_eff, passes, out_ids, out_scores, out_iscores, out_counts);
+    idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return LK_OK;
+}
+
+int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npos, const float *neg, const float *negw,
+                     int nneg, float beta, float lambda, int k, int scoring, const int32_t *allow_slots, int64_t n_allow,
+                     int64_t *out_ids, float *out_scores, int32_t *out_count) {
+    if (!idx || !out_count) return fail(LK_EINVAL, "lk_search_shared: bad argument");
+    *out_count = 0;
+    if (idx->store != LK_F32) return fail(LK_EINVAL, "lk_search_shared: needs float32 storage");
+    if (idx->comm) return fail(LK_EINVAL, "lk_search_shared: not available on a sharded index");
+    // constructor errors of embedvec.NewSharedQuery (media-server/embedvec/shared.go:62-70, :97-99)
+    if (npos <= 0 || !pos) return fail(LK_EINVAL, "embedvec: shared query has no positive terms");
+    if (nneg < 0 || (nneg > 0 && (!neg || !negw))) return fail(LK_EINVAL, "embedvec: shared query: negatives without weights");
+    if (allow_slots == nullptr && n_allow > 0) return fail(LK_EINVAL, "lk_search_shared: n_allow without allow_slots");
+    LK_TRY(use_device(idx));
+    LK_TRY(maybe_recenter(idx));
+    const bool centered = idx->center_live && scoring != LK_SCORE_PLAIN;
+    hm::SharedPrep sp;
+    const int pe = hm::shared_prepare(pos, posw, npos, neg, negw, nneg, idx->dim, beta, lambda,
+                                      centered ? idx->h_mu.data() : nullptr, &sp);
+    if (pe == 1) return fail(LK_EINVAL, "embedvec: shared query has no positive terms");
+    if (pe == 2) return fail(LK_EINVAL, "embedvec: shared query positive weight must be > 0");
+    const int T = sp.terms();
+    if (T > LK_SHARED_MAX_TERMS || sp.m * sp.rank > 256) return fail(LK_ERANGE, "lk_search_shared: more than 32 query-side vectors");
+    const bool filtered = allow_slots != nullptr;
+    const long long n_cand = filtered ? (long long)n_allow : idx->len;
+    if (filtered)
+        for (int64_t i = 0; i < n_allow; ++i)
+            if (allow_slots[i] < 0 || allow_slots[i] >= idx->len) return fail(LK_EINVAL, "lk_search_shared: allow slot out of range");
+    if (n_cand == 0 || k <= 0) return LK_OK;
+    const int k_eff = (int)std::min<long long>(k, n_cand);
+    const int passes = (k_eff + kMaxK - 1) / kMaxK;
+    const int k_pass = std::min(k_eff, kMaxK);
+    int err = 0;
+    const int grid = shared_scan_grid(T, idx->chunks, k_pass, idx->device, &err);
+    if (err == -1) return fail(LK_ERANGE, "lk_search_shared: terms x dim too large for shared memory");
+    if (err != 0 || grid <= 0) return fail(LK_ECUDA, std::string("shared scan occupancy query: ") + cudaGetErrorString((cudaError_t)err));
+    LK_TRY(idx->part.reserve((size_t)grid * k_pass * 8));
+    LK_TRY(idx->res.shape(1, k_eff, passes));
+    // upload: terms padded to the row width, then the scalar block
+    const size_t ldf = (size_t)idx->ld / 4;
+    const size_t terms_bytes = (size_t)T * ldf * 4;
+    const size_t par_off = (size_t)round_up((int64_t)terms_bytes, 16);
+    LK_TRY(idx->h_query.reserve(par_off + sizeof(SharedParams)));
+    LK_TRY(idx->d_query.reserve(par_off + sizeof(SharedParams)));
+    unsigned char *hq = (unsigned char *)idx->h_query.p;
+    memset(hq, 0, par_off + sizeof(SharedParams));
+    for (int t = 0; t < T; ++t)
+        memcpy(hq + (size_t)t * ldf * 4, &sp.vecs[(size_t)t * idx->dim], sizeof(float) * (size_t)idx->dim);
+    SharedParams *hp = reinterpret_cast<SharedParams *>(hq + par_off);
+    hp->m = sp.m;
+    hp->rank = sp.rank;
+    hp->nneg = sp.nneg;
+    hp->gamma = sp.gamma;
+    hp->lambda = sp.lambda;
+    for (int i = 0; i < sp.m; ++i) {
+        hp->posw[i] = sp.posw[i];
+        hp->posnorm[i] = sp.posnorm[i];
+    }
+    for (int i = 0; i < sp.nneg; ++i) hp->negw[i] = sp.negw[i];
+    for (int i = 0; i < sp.m * sp.rank; ++i) hp->qb[i] = sp.qb[i];
+    LK_CUDA(cudaMemcpyAsync(idx->d_query.p, hq, par_off + sizeof(SharedParams), cudaMemcpyHostToDevice, idx->stream));
+    const int *d_slots = nullptr;
+    if (filtered) {
+        LK_TRY(idx->d_slots.reserve((size_t)n_cand * 4));
+        LK_CUDA(cudaMemcpyAsync(idx->d_slots.p, allow_slots, (size_t)n_cand * 4, cudaMemcpyHostToDevice, idx->stream));
+        d_slots = (const int *)idx->d_slots.p;
+    }
+    for (int p = 0; p < passes; ++p) {
+        const int done = p * kMaxK;
+        SharedArgs a;
+        a.rows = idx->d_rows;
+        a.ld = idx->ld;
+        a.chunks = idx->chunks;
+        a.n = n_cand;
+        a.slots = d_slots;
+        a.terms = (const float *)idx->d_query.p;
+        a.params = (const SharedParams *)((const unsigned char *)idx->d_query.p + par_off);
+        a.cnorm = centered ? idx->d_cnorm : nullptr;
+        a.mu = idx->d_mu;
+        a.k = std::min(kMaxK, k_eff - done);
+        a.bound = (p == 0) ? nullptr : idx->res.d_keys() + done - 1;
+        a.part = (unsigned long long *)idx->part.p;
+        a.ticket = idx->d_ticket;
+        a.out_keys = idx->res.d_keys() + done;
+        a.out_ids = idx->res.d_ids() + done;
+        a.out_scores = idx->res.d_scores() + done;
+        a.out_iscores = idx->res.d_iscores() + done;
+        a.out_count = idx->res.d_counts() + p;
+        a.shard_base = idx->shard_base;
+        LK_TRY(shared_scan_launch(a, T, grid, idx->stream));
+        idx->scan_launches++;
+    }
+    LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    int32_t cnt = 0;
+    unpack_results(idx->res, 1, k, k_eff, passes, out_ids, out_scores, nullptr, &cnt);
+    *out_count = cnt;
+    return LK_OK;
+}
+
+// ---- device-resident queries ------------------------------------------------
+
+int lk_queries_create(lk_index *idx, const float *queries, int nq, int scoring, lk_queries **out) {
+    if (!idx || !out || nq <= 0 || !queries) return fail(LK_EINVAL, "lk_queries_create: bad argument");
+    *out = nullptr;
+    LK_TRY(use_device(idx));
+    LK_TRY(maybe_recenter(idx));
+    lk_queries *qs = new (std::nothrow) lk_queries();
+    if (!qs) return fail(LK_ENOMEM, "lk_queries_create: out of host memory");
+    qs->owner = idx;
+    qs->nq = nq;
+    qs->cq.resize((size_t)nq);
+    qs->qscale.resize((size_t)nq);
+    std::vector<unsigned char> host((size_t)nq * idx->qbytes);
+    for (int q = 0; q < nq; ++q) {
+        const bool c = prepare_query(idx, queries + (size_t)q * idx->dim, scoring, host.data() + (size_t)q * idx->qbytes,
+                                     &qs->cq[q], &qs->qscale[q]);
+        if (q == 0) qs->centered = c ? 1 : 0;
+    }
+    int st = qs->d_query.reserve(host.size());
+    if (st == 0) {
+        cudaError_t e = cudaMemcpy(qs->d_query.p, host.data(), host.size(), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) st = fail(LK_ECUDA, std::string("lk_queries_create: ") + cudaGetErrorString(e));
+    }
+    if (st != 0) {
+        lk_queries_destroy(qs);
+        return st;
+    }
+    *out = qs;
+    return LK_OK;
+}
+
+int lk_queries_destroy(lk_queries *q) {
+    if (!q) return LK_OK;
+    if (q->owner) cudaSetDevice(q->owner->device);
+    q->d_query.release();
+    q->res.release();
+    delete q;
+    return LK_OK;
+}
+
+int lk_search_resident(lk_index *idx, lk_queries *q, int first, int count, int k) {
+    if (!idx || !q || q->owner != idx || first < 0 || count < 0 || first + count > q->nq)
+        return fail(LK_EINVAL, "lk_search_resident: bad argument");
+    if (k <= 0 || k > kMaxK) return fail(LK_ERANGE, "lk_search_resident: k must be within 1..2048");
+    LK_TRY(use_device(idx));
+    const bool sharded = idx->comm != nullptr;
+    if ((idx->len == 0 && !sharded) || count == 0) return LK_OK;
+    const int k_eff = sharded ? k : (int)std::min<long long>(k, idx->len);
+    LK_TRY(ensure_scan_scratch(idx, k_eff));
+    if (q->res.nq != q->nq || q->res.k != k_eff) LK_TRY(q->res.shape(q->nq, k_eff, 1));
+    for (int i = first; i < first + count; ++i) {
+        LK_TRY(enqueue_query(idx, (const unsigned char *)q->d_query.p + (size_t)i * idx->qbytes, q->centered != 0,
+                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i));
+        // one query at a time: its candidates are exchanged and merged before the next scan starts
+        if (sharded) LK_TRY(comm_gather_merge(idx->comm, idx, q->res, i, 1, k_eff));
+    }
+    return LK_OK;
+}
+
+int lk_queries_fetch(lk_index *idx, lk_queries *q, int first, int count, int k, int64_t *out_ids, float *out_scores,
+                     int32_t *out_iscores, int32_t *out_counts) {
+    if (!idx || !q || q->owner != idx || first < 0 || count < 0 || first + count > q->nq)
+        return fail(LK_EINVAL, "lk_queries_fetch: bad argument");
+    LK_TRY(use_device(idx));
+    if (q->res.nq != q->nq || q->res.k <= 0) return fail(LK_EINVAL, "lk_queries_fetch: nothing has been searched yet");
+    LK_CUDA(cudaMemcpyAsync(q->res.host.p, q->res.dev.p, q->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    const ResultArena &r = q->res;
+    for (int i = 0; i < count; ++i) {
+        const int qi = first + i;
+        int cnt = std::min(r.h_counts()[qi], r.k);
+        for (int j = 0; j < k; ++j) {
+            const bool hit = j < cnt;
+            const size_t so = (size_t)qi * r.k + j, uo = (size_t)i * k + j;
+            if (out_ids) out_ids[uo] = hit ? (int64_t)r.h_ids()[so] : -1;
+            if (out_scores) out_scores[uo] = hit ? r.h_scores()[so] : 0.0f;
+            if (out_iscores) out_iscores[uo] = hit ? r.h_iscores()[so] : 0;
+        }
+        if (out_counts) out_counts[i] = cnt;
+    }
+    return LK_OK;
+}
+
+int lk_timer_start(lk_index *idx) {
+    if (!idx) return fail(LK_EINVAL, "lk_timer_start: idx is NULL");
+    LK_TRY(use_device(idx));
+    LK_CUDA(cudaEventRecord(idx->ev0, idx->stream));
+    return LK_OK;
+}
+
+int lk_timer_stop(lk_index *idx, float *elapsed_ms) {
+    if (!idx || !elapsed_ms) return fail(LK_EINVAL, "lk_timer_stop: bad argument");
+    LK_TRY(use_device(idx));
+    LK_CUDA(cudaEventRecord(idx->ev1, idx->stream));
+    LK_CUDA(cudaEventSynchronize(idx->ev1));
+    LK_CUDA(cudaEventElapsedTime(elapsed_ms, idx->ev0, idx->ev1));
+    return LK_OK;
+}
+
+int lk_index_sync(lk_index *idx) {
+    if (!idx) return fail(LK_EINVAL, "lk_index_sync: idx is NULL");
+    LK_TRY(use_device(idx));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    return LK_OK;
+}
+
+int lk_index_set_shard_base(lk_index *idx, int64_t shard_base) {
+    if (!idx || shard_base < 0) return fail(LK_EINVAL, "lk_index_set_shard_base: bad argument");
+    idx->shard_base = shard_base;
+    return LK_OK;
+}
+
+int lk_stats(lk_index *idx, lk_stats_t *out) {
+    if (!idx || !out) return fail(LK_EINVAL, "lk_stats: bad argument");
+    out->len = idx->len;
+    out->capacity = idx->cap;
+    out->bytes_resident = (int64_t)idx->cap * idx->ld + (idx->d_scales ? idx->cap * 4 : 0) + (idx->d_cnorm ? idx->cap * 4 : 0) +
+                          (int64_t)idx->part.bytes + (int64_t)idx->res.dev.bytes + (int64_t)idx->d_query.bytes +
+                          (int64_t)idx->d_slots.bytes + (int64_t)idx->d_stage.bytes + (int64_t)idx->gather.bytes;
+    out->scan_launches = idx->scan_launches;
+    out->aux_launches = idx->aux_launches;
+    out->last_search_ms = idx->last_search_ms;
+    out->grid = idx->grid;
+    out->sm_count = idx->sm_count;
+    return LK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+// Exact top-k selection inside a CTA, fused into the kernels that produce scores.
+//
+// Every scoring kernel turns a score into a 64-bit ranking key (lk_common.cuh) and
+// offers it to a per-CTA candidate buffer in shared memory.  A key is stored only
+// if it beats the CTA's current threshold (the k-th best key seen so far), so after
+// a short warm-up almost every row costs one compare.  When the buffer runs full
+// the CTA sorts it (bitonic, in shared memory), keeps the best k and raises the
+// threshold.  Scores therefore never travel to HBM: a CTA writes k keys at the end,
+// and the last CTA to finish merges all CTAs' lists with the same machinery.
+//
+// This replaces the reference's "materialise N float32 scores, then run a serial
+// size-k min-heap over them" (media-server/embedindex/embedindex.go:432, :495-534)
+// and its final sort (media-server/embedindex/embedindex.go:483-490).
+#pragma once
+#include "lk_common.cuh"
+
+namespace lk {
+
+constexpr int kScanThreads = 256;           // threads per scan CTA
+constexpr int kScanWarps = kScanThreads / 32;
+constexpr int kMaxK = 2048;                 // largest k one pass selects; larger k runs more passes
+
+// Buffer capacity for a given k: room for k survivors plus one full round of
+// appends from every warp (32 keys each) after the "nearly full" mark is passed.
+__host__ __device__ inline int cand_capacity(int k) {
+    int need = k + kScanThreads;
+    int cap = 512;
+    while (cap < need) cap <<= 1;
+    return cap;
+}
+
+struct CandCtrl {
+    int count;               // keys currently in the buffer
+    int n_done;              // warps that have no rows left
+    unsigned long long thr;  // keys must be strictly greater than this to enter
+};
+
+struct CandBuf {
+    unsigned long long *keys;  // [cap] shared memory
+    CandCtrl *ctrl;            // shared memory
+    int cap;
+    int limit;                 // prune once count exceeds this (= cap - kScanThreads)
+    int k;
+};
+
+// Sort keys[0..count) descending, keep the best k, zero the rest, refresh thr.
+// Must be called by all threads of the CTA with `count` stable.
+__device__ inline void cand_prune(const CandBuf &b) {
+    const int tid = threadIdx.x, T = blockDim.x;
+    const int c = b.ctrl->count;
+    int sz = 2;
+    while (sz < c) sz <<= 1;
+    for (int i = c + tid; i < sz; i += T) b.keys[i] = 0ull;
+    __syncthreads();
+    for (int size = 2; size <= sz; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < (sz >> 1); i += T) {
+                int pos = 2 * i - (i & (stride - 1));
+                unsigned long long x = b.keys[pos], y = b.keys[pos + stride];
+                bool desc = (pos & size) == 0;
+                if ((x < y) == desc) {
+                    b.keys[pos] = y;
+                    b.keys[pos + stride] = x;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    const int keep = c < b.k ? c : b.k;
+    for (int i = keep + tid; i < sz; i += T) b.keys[i] = 0ull;
+    if (tid == 0) {
+        b.ctrl->count = keep;
+        b.ctrl->thr = (keep == b.k) ? b.keys[b.k - 1] : 0ull;
+    }
+    __syncthreads();
+}
+
+// Warp-aggregated append: lanes with pass==true store their key.  The caller has
+// checked count <= limit before producing this batch, which leaves room for one
+// batch from every warp.
+__device__ __forceinline__ void cand_offer_warp(const CandBuf &b, bool pass, unsigned long long key) {
+    const unsigned m = __ballot_sync(0xffffffffu, pass);
+    if (m == 0) return;
+    const int lane = threadIdx.x & 31;
+    const int leader = __ffs(m) - 1;
+    int base = 0;
+    if (lane == leader) base = atomicAdd(&b.ctrl->count, __popc(m));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (pass) b.keys[base + __popc(m & lanemask_lt())] = key;
+}
+
+// Select the best k of a list of keys in global memory (zeros are skipped) into
+// the buffer, sorted descending.  All threads of the CTA call this in lockstep.
+__device__ inline void cand_select_from_global(const CandBuf &b, const unsigned long long *src,
+                                               long long total) {
+    const int tid = threadIdx.x, T = blockDim.x;
+    for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
+    if (tid == 0) {
+        b.ctrl->count = 0;
+        b.ctrl->thr = 0ull;
+    }
+    __syncthreads();
+    for (long long base = 0; base < total; base += T) {
+        long long i = base + tid;
+        unsigned long long key = (i < total) ? __ldcg(src + i) : 0ull;
+        if (key > *(volatile unsigned long long *)&b.ctrl->thr) {
+            int pos = atomicAdd(&b.ctrl->count, 1);
+            b.keys[pos] = key;
+        }
+        __syncthreads();
+        if (b.ctrl->count > b.limit) cand_prune(b);  // uniform: count is stable after the barrier
+    }
+    cand_prune(b);
+}
+
+}  // namespace lk
