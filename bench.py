@@ -151,13 +151,13 @@ def run_reference(args):
     qps, cores, desc, per_q = cpu_reference_scan(steps, min(args.warmup, 3))
     line = {
         "impl": "reference", "metric": "queries/sec, top-10 scan of 1M x 768 rows per GPU shard",
-        "value": qps * args.gpus, "unit": "queries/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
+        "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
         "ms_per_step": per_q * 1e3 * ROWS_PER_GPU / 100_000, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": "1,000,000 x 768 rows, single queries, top-10 (reference stores float32, accumulates float64)",
-                   "note": "CPU path does not use GPUs; value x n_gpus keeps the unit of the GPU arm (shard scans/s)"},
+                   "note": "CPU path, no GPU used; unit = scans of one 1M-row shard per second, the same unit as the GPU arm at any N"},
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": desc},
-        "e2e": {"value": qps * args.gpus, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
