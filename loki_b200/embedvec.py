@@ -1,0 +1,36 @@
+"""The BLOB codec of ``media-server/embedvec`` for callers that feed this library.
+
+Vectors are stored by the server as little-endian float32 BLOBs
+(``media-server/embedvec/embedvec.go:12-31``; tables ``media_embedding.vector`` and
+``face.vector``).  ``decode_rows`` turns a batch of BLOBs into the row matrix that
+``VectorIndex.AddBatch`` / ``lk_index_upsert_f32`` take.  Scoring itself never runs
+here: it runs on the GPU.
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+import numpy as np
+
+
+def Encode(v) -> bytes:
+    """media-server/embedvec/embedvec.go:13-19."""
+    return np.ascontiguousarray(v, dtype=np.float32).astype("<f4").tobytes()
+
+
+def Decode(b: bytes) -> np.ndarray:
+    """media-server/embedvec/embedvec.go:22-31: rejects lengths that are not a multiple of 4."""
+    if len(b) % 4 != 0:
+        raise ValueError(f"embedvec: byte length {len(b)} is not a multiple of 4")
+    return np.frombuffer(b, dtype="<f4").astype(np.float32)
+
+
+def decode_rows(blobs: Iterable[bytes], dim: int) -> np.ndarray:
+    """Decode BLOBs into an (n, dim) float32 matrix; a BLOB of another length becomes
+    a zero row (it can never match: Cosine returns 0 on a length mismatch)."""
+    blobs = list(blobs)
+    out = np.zeros((len(blobs), dim), np.float32)
+    for i, b in enumerate(blobs):
+        if len(b) == dim * 4:
+            out[i] = np.frombuffer(b, dtype="<f4")
+    return out
