@@ -159,11 +159,8 @@ static bool prepare_query(const lk_index *idx, const float *q, int scoring, unsi
 
 static int ensure_scan_scratch(lk_index *idx, int k) {
     if (idx->grid_for_k != k) {
-        int err = 0;
-        const int g = scan_resident_grid(idx->type, idx->chunks, k, idx->device, &err);
-        if (err != 0 || g <= 0)
-            return fail(LK_ECUDA, std::string("scan occupancy query: ") + cudaGetErrorString((cudaError_t)err));
-        idx->grid = g;
+        LK_TRY(scan_plan(idx->type, idx->chunks, k, idx->device, &idx->plan));
+        idx->grid = scan_max_grid(idx->plan);
         idx->grid_for_k = k;
     }
     LK_TRY(idx->part.reserve((size_t)idx->grid * k * 8));
@@ -192,6 +189,7 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
         a.bound = (p == 0) ? nullptr : res.d_keys() + o - 1;
         a.part = (unsigned long long *)idx->part.p;
         a.ticket = idx->d_ticket;
+        a.error = (int *)(idx->d_ticket + 1);
         a.out_keys = res.d_keys() + o;
         a.out_ids = res.d_ids() + o;
         a.out_scores = res.d_scores() + o;
@@ -200,14 +198,18 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
         a.scales = idx->d_scales;
         a.qscale = qscale;
         a.shard_base = idx->shard_base;
-        LK_TRY(scan_launch(idx->type, a, idx->grid, idx->stream));
+        LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream));
         idx->scan_launches++;
     }
     return 0;
 }
 
-static void unpack_results(const ResultArena &res, int nq, int k_user, int k_eff, int passes,
-                           int64_t *out_ids, float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+static int unpack_results(const ResultArena &res, int nq, int k_user, int k_eff, int passes,
+                          int64_t *out_ids, float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+    for (int q = 0; q < nq; ++q)
+        for (int p = 0; p < passes; ++p)
+            if (res.h_counts()[(size_t)q * passes + p] < 0)
+                return fail(LK_ETIMEOUT, "a scan kernel gave up waiting for a bulk copy into shared memory; results are not valid");
     for (int q = 0; q < nq; ++q) {
         int cnt = 0;
         for (int p = 0; p < passes; ++p) cnt += res.h_counts()[(size_t)q * passes + p];
@@ -221,6 +223,7 @@ static void unpack_results(const ResultArena &res, int nq, int k_user, int k_eff
         }
         if (out_counts) out_counts[q] = cnt;
     }
+    return 0;
 }
 
 }  // namespace lk
@@ -452,7 +455,7 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     if (sharded) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
     LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
-    unpack_results(idx->res, nq, k, k_eff, passes, out_ids, out_scores, out_iscores, out_counts);
+    LK_TRY(unpack_results(idx->res, nq, k, k_eff, passes, out_ids, out_scores, out_iscores, out_counts));
     idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return LK_OK;
 }
@@ -550,7 +553,7 @@ int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npo
     LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
     int32_t cnt = 0;
-    unpack_results(idx->res, 1, k, k_eff, passes, out_ids, out_scores, nullptr, &cnt);
+    LK_TRY(unpack_results(idx->res, 1, k, k_eff, passes, out_ids, out_scores, nullptr, &cnt));
     *out_count = cnt;
     return LK_OK;
 }
@@ -626,6 +629,8 @@ int lk_queries_fetch(lk_index *idx, lk_queries *q, int first, int count, int k, 
     const ResultArena &r = q->res;
     for (int i = 0; i < count; ++i) {
         const int qi = first + i;
+        if (r.h_counts()[qi] < 0)
+            return fail(LK_ETIMEOUT, "a scan kernel gave up waiting for a bulk copy into shared memory; results are not valid");
         int cnt = std::min(r.h_counts()[qi], r.k);
         for (int j = 0; j < k; ++j) {
             const bool hit = j < cnt;

@@ -6,6 +6,7 @@
 
 #include "../../include/lokiscan.h"
 #include "lk_common.cuh"
+#include "scan.cuh"
 
 namespace lk {
 
@@ -123,6 +124,7 @@ struct lk_index {
     lk::DevBuf part;
     unsigned int *d_ticket = nullptr;
     int grid_for_k = -1, grid = 0;
+    lk::ScanPlan plan;
     // per-call buffers
     lk::ResultArena res;
     lk::DevBuf d_query, d_slots, d_stage;

@@ -19,11 +19,12 @@ struct ScanArgs {
     const unsigned long long *bound;  // nullptr, or exclusive upper bound on accepted keys
     unsigned long long *part;   // scratch [grid][k]: per-CTA candidate lists
     unsigned int *ticket;       // scratch: CTAs finished so far (self-resetting)
+    int *error;                 // scratch: raised by a CTA whose bounded wait ran out (self-resetting)
     unsigned long long *out_keys;  // [k] ranked keys, zero padded
     long long *out_ids;         // [k] shard_base + slot, -1 padded
     float *out_scores;          // [k]
     int *out_iscores;           // [k] or nullptr (int8: raw dots)
-    int *out_count;             // hits written
+    int *out_count;             // hits written; -1 when a bounded device-side wait ran out
     const float *scales;        // int8: per-slot scale
     float qscale;               // int8: scale of the query
     long long shard_base;
@@ -31,13 +32,28 @@ struct ScanArgs {
 
 enum ScanType { SCAN_F32 = 0, SCAN_F16 = 1, SCAN_I8 = 2 };
 
-// Bytes of prepared-query data per 16-byte corpus chunk as it sits in global memory.
+// Bytes of one prepared query as it sits in global memory.
 int scan_query_bytes(int type, long long ld);
-// Lane-group width the launcher will use for this row width.
+// Lane-group width used for rows of this many 16-byte chunks.
 int scan_group_width(int chunks);
-// CTAs that fit on the device at once for this configuration (grid size to launch).
-int scan_resident_grid(int type, int chunks, int k, int device, int *err);
-int scan_launch(int type, const ScanArgs &a, int grid, cudaStream_t stream);
+
+// Launch configuration of both scan kernels for one (storage type, row width, k).
+struct ScanPlan {
+    // register-staged kernel (any input, allow-lists)
+    int g = 32;            // lane-group width
+    int grid = 1;          // CTAs resident at once
+    size_t smem = 0;
+    // TMA-staged kernel (whole contiguous rows)
+    bool bulk_ok = false;
+    int bulk_g = 32;
+    int bulk_grid = 1;     // one CTA per SM
+    int slab_bytes = 0;    // bytes of each row held per stage
+    int n_slabs = 1;       // stages per 32-row batch
+    size_t bulk_smem = 0;
+};
+int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan);
+int scan_max_grid(const ScanPlan &plan);   // CTAs to size the per-CTA list scratch for
+int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream);
 
 // Merge, for each of nq queries, `lists` ranked key lists of k entries each (global
 // memory, zero padded) into one ranked result of k entries at out_*[q*k];

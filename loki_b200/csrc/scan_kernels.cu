@@ -27,6 +27,8 @@
 // buffer is nearly full (to prune it) and when they run out of rows.
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "scan.cuh"
 #include "topk.cuh"
 
@@ -178,13 +180,115 @@ __device__ __forceinline__ void emit_hit(int type, unsigned long long key, int i
 }
 
 // ---------------------------------------------------------------------------
-// The scan kernel
+// One batch of (up to) 32 rows -> lane i holds the finished accumulator of row i.
+// `row_ptr(i)` gives the address of batch row i (global or shared memory), `row_ok(i)`
+// whether it exists; Load fetches 16 bytes from that address space.
+// ---------------------------------------------------------------------------
+struct LoadGlobal {
+    __device__ __forceinline__ static int4 ld(const unsigned char *p) { return ld_stream16(p); }
+};
+struct LoadShared {
+    __device__ __forceinline__ static int4 ld(const unsigned char *p) { return *reinterpret_cast<const int4 *>(p); }
+};
+
+// acc[t] += <row (grp*G + t) of the batch, query> over chunks [0, n_chunks) of the rows
+// as laid out at row_ptr(i); q_chunk0 is the index of the first of those chunks in the query.
+template <class TR, int G, int R, class Load, class RowPtr, class RowOk>
+__device__ __forceinline__ void batch_accumulate(typename TR::acc_t (&acc)[G], const unsigned char *qs, int q_chunks,
+                                                 int q_chunk0, int n_chunks, int lane, RowPtr row_ptr, RowOk row_ok) {
+    const int grp = lane / G, gl = lane % G;
+#pragma unroll
+    for (int t0 = 0; t0 < G; t0 += R) {
+        const unsigned char *p[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int in_batch = grp * G + t0 + r;
+            ok[r] = row_ok(in_batch);
+            p[r] = row_ptr(in_batch);
+        }
+#pragma unroll 2
+        for (int j = gl; j < n_chunks; j += G) {
+            const typename TR::QChunk qc = TR::load_q(qs, q_chunk0 + j, q_chunks);
+            int4 v[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) v[r] = ok[r] ? Load::ld(p[r] + (size_t)j * 16) : make_int4(0, 0, 0, 0);
+#pragma unroll
+            for (int r = 0; r < R; ++r) TR::dot(acc[t0 + r], v[r], qc);
+        }
+    }
+}
+
+// transposed butterfly: lane i of the warp ends with the total of batch row i (in acc[0])
+template <class TR, int G>
+__device__ __forceinline__ typename TR::acc_t batch_reduce(typename TR::acc_t (&acc)[G], int lane) {
+    using acc_t = typename TR::acc_t;
+#pragma unroll
+    for (int w = G / 2; w >= 1; w >>= 1) {
+        const bool upper = (lane & w) != 0;
+#pragma unroll
+        for (int i = 0; i < w; ++i) {
+            const acc_t send = upper ? acc[i] : acc[i + w];
+            const acc_t keep = upper ? acc[i + w] : acc[i];
+            acc[i] = keep + TR::shfl(send, w);
+        }
+    }
+    return acc[0];
+}
+
+// Shared tail of both scan kernels: publish this CTA's list; the last CTA to arrive
+// merges all lists and writes the result.
+template <int TYPE>
+__device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const CandBuf &buf, int *s_last) {
+    const int tid = threadIdx.x, T = blockDim.x;
+    unsigned long long *mine = a.part + (size_t)blockIdx.x * a.k;
+    for (int i = tid; i < a.k; i += T) mine[i] = buf.keys[i];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) *s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    cand_select_from_lists(buf, a.part, (int)gridDim.x);
+    const int cnt = buf.ctrl->count;
+    for (int i = tid; i < a.k; i += T) {
+        const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
+        a.out_keys[i] = key;
+        float dq = 0.0f;
+        if (TYPE == SCAN_I8 && key != 0ull) dq = a.qscale * a.scales[key_slot(key)];
+        emit_hit(TYPE, key, i, a.shard_base, dq, a.out_ids, a.out_scores, a.out_iscores);
+    }
+    if (tid == 0) {
+        // a CTA whose bounded wait ran out has raised the flag before publishing its list
+        const bool bad = a.error != nullptr && *(volatile int *)a.error != 0;
+        *a.out_count = bad ? -1 : cnt;
+        if (bad) *a.error = 0;
+        *a.ticket = 0u;
+    }
+}
+
+// The meeting point of the free-running warps (see the header comment): returns
+// true when every warp is out of rows and the buffer holds the CTA's final list.
+__device__ __forceinline__ bool cand_rendezvous(const CandBuf &buf, bool work, bool &counted, int lane, int nwarps) {
+    if (!work && !counted) {
+        if (lane == 0) atomicAdd(&buf.ctrl->n_done, 1);
+        counted = true;
+    }
+    __syncthreads();  // nobody appends past this point
+    const int c = buf.ctrl->count, nd = buf.ctrl->n_done;
+    __syncthreads();  // everybody has read the same state
+    if (c > buf.limit || nd == nwarps) cand_prune(buf);
+    return nd == nwarps;
+}
+
+// ---------------------------------------------------------------------------
+// Scan kernel, register-staged: every lane loads its 16-byte chunks straight from
+// global memory.  Used for allow-list (gathered) scans and for small inputs.
 // ---------------------------------------------------------------------------
 template <class TR, int TYPE, int G>
 __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const ScanArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int R = (G < TR::kRows) ? G : TR::kRows;
-    using acc_t = typename TR::acc_t;
 
     CandBuf buf;
     buf.k = a.k;
@@ -209,7 +313,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const ScanArgs a) {
     const long long n_batches = (a.n + 31) >> 5;
     const long long b_lo = n_batches * blockIdx.x / gridDim.x;
     const long long b_hi = n_batches * (blockIdx.x + 1) / gridDim.x;
-    const int grp = lane / G, gl = lane % G;
 
     long long b = b_lo + warp;
     bool counted = false;
@@ -223,87 +326,198 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const ScanArgs a) {
             const long long row0 = b << 5;
             int myslot = 0;
             if (a.slots != nullptr && row0 + lane < a.n) myslot = a.slots[row0 + lane];
-            acc_t acc[G];
+            typename TR::acc_t acc[G];
 #pragma unroll
-            for (int t = 0; t < G; ++t) acc[t] = (acc_t)0;
-#pragma unroll
-            for (int t0 = 0; t0 < G; t0 += R) {
-                const unsigned char *p[R];
-                bool ok[R];
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int in_batch = grp * G + t0 + r;
-                    const long long rr = row0 + in_batch;
-                    ok[r] = rr < a.n;
-                    long long srow = rr;
-                    if (a.slots != nullptr) srow = __shfl_sync(0xffffffffu, myslot, in_batch);
-                    p[r] = a.rows + (ok[r] ? srow : 0) * a.ld;
-                }
-#pragma unroll 2
-                for (int j = gl; j < a.chunks; j += G) {
-                    const typename TR::QChunk qc = TR::load_q(qs, j, a.chunks);
-                    int4 v[R];
-#pragma unroll
-                    for (int r = 0; r < R; ++r)
-                        v[r] = ok[r] ? ld_stream16(p[r] + (size_t)j * 16) : make_int4(0, 0, 0, 0);
-#pragma unroll
-                    for (int r = 0; r < R; ++r) TR::dot(acc[t0 + r], v[r], qc);
-                }
-            }
-            // transposed butterfly: lane i of the group ends with the total of row i
-#pragma unroll
-            for (int w = G / 2; w >= 1; w >>= 1) {
-                const bool upper = (lane & w) != 0;
-#pragma unroll
-                for (int i = 0; i < w; ++i) {
-                    const acc_t send = upper ? acc[i] : acc[i + w];
-                    const acc_t keep = upper ? acc[i + w] : acc[i];
-                    acc[i] = keep + TR::shfl(send, w);
-                }
-            }
+            for (int t = 0; t < G; ++t) acc[t] = (typename TR::acc_t)0;
+            batch_accumulate<TR, G, R, LoadGlobal>(
+                acc, qs, a.chunks, 0, a.chunks, lane,
+                [&](int i) -> const unsigned char * {
+                    long long srow = row0 + i;
+                    if (a.slots != nullptr) srow = __shfl_sync(0xffffffffu, myslot, i);
+                    return a.rows + ((row0 + i < a.n) ? srow : 0) * a.ld;
+                },
+                [&](int i) -> bool { return row0 + i < a.n; });
+            const typename TR::acc_t total = batch_reduce<TR, G>(acc, lane);
             const long long rr = row0 + lane;
             const bool valid = rr < a.n;
             const unsigned slot = (a.slots != nullptr) ? (unsigned)myslot : (unsigned)rr;
             unsigned long long key = 0ull;
-            if (valid) key = make_key(TR::finish(acc[0], a, slot), slot);
+            if (valid) key = make_key(TR::finish(total, a, slot), slot);
             const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
             cand_offer_warp(buf, valid && key > thr && key < bound, key);
             b += kScanWarps;
             continue;
         }
-        if (!work && !counted) {
-            if (lane == 0) atomicAdd(&buf.ctrl->n_done, 1);
-            counted = true;
-        }
-        __syncthreads();  // nobody appends past this point
-        const int c = buf.ctrl->count, nd = buf.ctrl->n_done;
-        __syncthreads();  // everybody has read the same state
-        if (c > buf.limit || nd == kScanWarps) cand_prune(buf);
-        if (nd == kScanWarps) break;
+        if (cand_rendezvous(buf, work, counted, lane, kScanWarps)) break;
     }
+    publish_and_finish<TYPE>(a, buf, &s_last);
+}
 
-    // ---- publish this CTA's list; the last CTA to arrive merges all lists ----
-    unsigned long long *mine = a.part + (size_t)blockIdx.x * a.k;
-    for (int i = tid; i < a.k; i += kScanThreads) mine[i] = buf.keys[i];
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    cand_select_from_global(buf, a.part, (long long)gridDim.x * a.k);
-    const int cnt = buf.ctrl->count;
-    for (int i = tid; i < a.k; i += kScanThreads) {
-        const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
-        a.out_keys[i] = key;
-        float dq = 0.0f;
-        if (TYPE == SCAN_I8 && key != 0ull) dq = a.qscale * a.scales[key_slot(key)];
-        emit_hit(TYPE, key, i, a.shard_base, dq, a.out_ids, a.out_scores, a.out_iscores);
-    }
+// ---------------------------------------------------------------------------
+// Scan kernel, TMA-staged: the corpus is streamed into shared memory with bulk
+// asynchronous copies (cp.async.bulk, completion on an mbarrier), 32 rows
+// (32 x ld contiguous bytes) per tile.  One CTA per SM; every warp owns kStages
+// private tile buffers, reads a tile with conflict-free 16-byte shared loads and,
+// as soon as it has consumed it, issues the copy of its next tile into the same
+// buffer.  Bytes in flight per SM = warps x (kStages-1..kStages) x tile, independent
+// of register pressure, which is what it takes to keep HBM3e busy from 148 SMs.
+// ---------------------------------------------------------------------------
+constexpr int kBulkStages = 2;
+constexpr unsigned kBulkSpinLimit = 1u << 22;  // bounded wait on a tile (each try blocks briefly in hardware)
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// global -> shared bulk copy; bytes and both addresses are multiples of 16
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+template <class TR, int TYPE, int G, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, int slab_bytes, int n_slabs) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int R = (G < 4) ? G : 4;  // shared-memory latency is short: few rows in flight suffice
+    constexpr int T = WARPS * 32;
+    using acc_t = typename TR::acc_t;
+
+    CandBuf buf;
+    buf.k = a.k;
+    buf.cap = cand_capacity(a.k);
+    buf.limit = buf.cap - kScanThreads;
+    buf.keys = reinterpret_cast<unsigned long long *>(smem);
+    buf.ctrl = reinterpret_cast<CandCtrl *>(smem + (size_t)buf.cap * 8);
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem + (size_t)buf.cap * 8 + 16);
+    unsigned char *qs = smem + (size_t)buf.cap * 8 + 16 + WARPS * kBulkStages * 8;
+    const size_t stage_bytes = (size_t)32 * slab_bytes;
+    const size_t q_bytes = (size_t)a.chunks * TR::kQBytes;
+    unsigned char *stages = smem + (((size_t)buf.cap * 8 + 16 + WARPS * kBulkStages * 8 + q_bytes + 127) & ~(size_t)127);
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < buf.cap; i += T) buf.keys[i] = 0ull;
     if (tid == 0) {
-        *a.out_count = cnt;
-        *a.ticket = 0u;
+        buf.ctrl->count = 0;
+        buf.ctrl->n_done = 0;
+        buf.ctrl->thr = 0ull;
+        for (int i = 0; i < WARPS * kBulkStages; ++i) mbar_init(&bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    TR::stage_query(qs, a.query, a.chunks);
+    const unsigned long long bound = a.bound ? __ldcg(a.bound) : ~0ull;
+    __syncthreads();
+
+    const long long n_batches = (a.n + 31) >> 5;
+    const long long b_lo = n_batches * blockIdx.x / gridDim.x;
+    const long long b_hi = n_batches * (blockIdx.x + 1) / gridDim.x;
+    unsigned char *my_stages = stages + (size_t)warp * kBulkStages * stage_bytes;
+    unsigned long long *my_bars = bars + warp * kBulkStages;
+
+    // Item m of this warp = (batch b_lo + warp + (m / n_slabs) * WARPS, slab m % n_slabs); it
+    // lives in stage m % kBulkStages.  A slab is a column range of slab_bytes of each row
+    // (the last one may be narrower); rows are packed slab_w bytes apart in the stage.
+    auto slab_width = [&](int sl) -> int { return min(slab_bytes, (int)a.ld - sl * slab_bytes); };
+    auto issue = [&](long long m) {  // called by the whole warp
+        const long long b = b_lo + warp + (m / n_slabs) * WARPS;
+        if (b >= b_hi) return;
+        const int sl = (int)(m % n_slabs);
+        const long long row0 = b << 5;
+        const int rows = (int)min(32ll, a.n - row0);
+        const int w = slab_width(sl);
+        const int s = (int)(m % kBulkStages);
+        unsigned char *dst = my_stages + (size_t)s * stage_bytes;
+        if (lane == 0) mbar_expect_tx(&my_bars[s], (unsigned)(rows * w));
+        __syncwarp();
+        if (n_slabs == 1) {  // whole rows: the batch is one contiguous range
+            if (lane == 0) bulk_load(dst, a.rows + (size_t)row0 * a.ld, (unsigned)(rows * w), &my_bars[s]);
+        } else if (lane < rows) {  // one row segment per lane
+            bulk_load(dst + (size_t)lane * w, a.rows + (size_t)(row0 + lane) * a.ld + (size_t)sl * slab_bytes,
+                      (unsigned)w, &my_bars[s]);
+        }
+    };
+    for (int m = 0; m < kBulkStages; ++m) issue(m);
+
+    long long m = 0;
+    bool counted = false, failed = false;
+    acc_t acc[G];
+    for (;;) {
+        const long long b = b_lo + warp + (m / n_slabs) * WARPS;
+        const int sl = (int)(m % n_slabs);
+        const bool work = b < b_hi && !failed;
+        int seen = 0;
+        if (lane == 0) seen = *(volatile int *)&buf.ctrl->count;
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        // the buffer is only looked at between batches: a batch in progress always finishes
+        if (work && (sl != 0 || seen <= buf.limit)) {
+            const int s = (int)(m % kBulkStages);
+            const unsigned parity = (unsigned)((m / kBulkStages) & 1);
+            // bounded wait for the data; on expiry flag the error and stop taking work
+            unsigned spins = 0;
+            bool ready = false;
+            while (!(ready = mbar_try_wait(&my_bars[s], parity)) && ++spins < kBulkSpinLimit) {}
+            if (!__all_sync(0xffffffffu, ready)) {
+                if (lane == 0 && a.error != nullptr) atomicExch(a.error, 1);
+                failed = true;
+                continue;
+            }
+            const long long row0 = b << 5;
+            const int rows = (int)min(32ll, a.n - row0);
+            const int w = slab_width(sl);
+            const unsigned char *stage = my_stages + (size_t)s * stage_bytes;
+            if (sl == 0) {
+#pragma unroll
+                for (int t = 0; t < G; ++t) acc[t] = (acc_t)0;
+            }
+            batch_accumulate<TR, G, R, LoadShared>(
+                acc, qs, a.chunks, sl * (slab_bytes >> 4), w >> 4, lane,
+                [&](int i) -> const unsigned char * { return stage + (size_t)(i < rows ? i : 0) * w; },
+                [&](int i) -> bool { return i < rows; });
+            // every lane has its part of the stage in registers (the accumulators depend on
+            // it): the stage is free, refill it with this warp's item m + kBulkStages
+            __syncwarp();
+            issue(m + kBulkStages);
+            ++m;
+            if (sl != n_slabs - 1) continue;
+            const acc_t total = batch_reduce<TR, G>(acc, lane);
+            const bool valid = lane < rows;
+            const unsigned slot = (unsigned)(row0 + lane);
+            unsigned long long key = 0ull;
+            if (valid) key = make_key(TR::finish(total, a, slot), slot);
+            const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
+            cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            continue;
+        }
+        if (cand_rendezvous(buf, work, counted, lane, WARPS)) break;
+    }
+    // A warp that gave up may still have copies in flight into its stages: wait for
+    // them (bounded) before the CTA's shared memory is released.
+    if (failed) {
+        for (long long mm = m; mm < m + kBulkStages; ++mm) {
+            if (b_lo + warp + (mm / n_slabs) * WARPS >= b_hi) break;
+            unsigned spins = 0;
+            while (!mbar_try_wait(&my_bars[mm % kBulkStages], (unsigned)((mm / kBulkStages) & 1)) &&
+                   ++spins < kBulkSpinLimit) {}
+        }
+    }
+    publish_and_finish<TYPE>(a, buf, &s_last);
 }
 
 // ---------------------------------------------------------------------------
@@ -335,7 +549,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_merge_lists(const MergeArgs
     }
     __threadfence_block();
     __syncthreads();
-    cand_select_from_global(buf, scratch, total);
+    cand_select_from_lists(buf, scratch, a.lists);
     const int cnt = buf.ctrl->count;
     for (int i = tid; i < a.k; i += kScanThreads) {
         const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
@@ -397,12 +611,16 @@ int scan_query_bytes(int type, long long ld) {
     }
 }
 
-static size_t scan_smem_bytes(int type, int chunks, int k) {
-    const int qb = (type == SCAN_I8) ? TraitsI8::kQBytes : (type == SCAN_F32 ? TraitsF32::kQBytes : TraitsF16::kQBytes);
-    return (size_t)cand_capacity(k) * 8 + 16 + (size_t)chunks * qb;
+static int q_smem_per_chunk(int type) {
+    return (type == SCAN_I8) ? TraitsI8::kQBytes : (type == SCAN_F32 ? TraitsF32::kQBytes : TraitsF16::kQBytes);
 }
 
+constexpr int kBulkWarps = 4;
+constexpr int kBulkSlabMax = 768;               // bytes of one row kept per stage: 32 rows x 768 B = 24 KB
+constexpr size_t kSmemLimit = 227 * 1024;
+
 typedef void (*scan_fn)(const ScanArgs);
+typedef void (*bulk_fn)(const ScanArgs, int, int);
 
 template <class TR, int TYPE>
 static scan_fn pick_g(int g) {
@@ -415,7 +633,6 @@ static scan_fn pick_g(int g) {
         default: return k_scan<TR, TYPE, 32>;
     }
 }
-
 static scan_fn pick(int type, int g) {
     switch (type) {
         case SCAN_I8: return pick_g<TraitsI8, SCAN_I8>(g);
@@ -423,34 +640,80 @@ static scan_fn pick(int type, int g) {
         default: return pick_g<TraitsF16, SCAN_F16>(g);
     }
 }
-
-int scan_resident_grid(int type, int chunks, int k, int device, int *err) {
-    *err = 0;
-    scan_fn fn = pick(type, scan_group_width(chunks));
-    const size_t smem = scan_smem_bytes(type, chunks, k);
-    cudaError_t e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { *err = (int)e; return 0; }
-    int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void *)fn, kScanThreads, smem);
-    if (e != cudaSuccess) { *err = (int)e; return 0; }
-    int sms = 0;
-    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    if (e != cudaSuccess) { *err = (int)e; return 0; }
-    if (per_sm < 1) per_sm = 1;
-    return per_sm * sms;
+template <class TR, int TYPE>
+static bulk_fn pick_bulk_g(int g) {
+    switch (g) {
+        case 1: return k_scan_bulk<TR, TYPE, 1, kBulkWarps>;
+        case 2: return k_scan_bulk<TR, TYPE, 2, kBulkWarps>;
+        case 4: return k_scan_bulk<TR, TYPE, 4, kBulkWarps>;
+        case 8: return k_scan_bulk<TR, TYPE, 8, kBulkWarps>;
+        case 16: return k_scan_bulk<TR, TYPE, 16, kBulkWarps>;
+        default: return k_scan_bulk<TR, TYPE, 32, kBulkWarps>;
+    }
+}
+static bulk_fn pick_bulk(int type, int g) {
+    switch (type) {
+        case SCAN_I8: return pick_bulk_g<TraitsI8, SCAN_I8>(g);
+        case SCAN_F32: return pick_bulk_g<TraitsF32, SCAN_F32>(g);
+        default: return pick_bulk_g<TraitsF16, SCAN_F16>(g);
+    }
 }
 
-int scan_launch(int type, const ScanArgs &a, int grid, cudaStream_t stream) {
-    scan_fn fn = pick(type, scan_group_width(a.chunks));
-    const size_t smem = scan_smem_bytes(type, a.chunks, a.k);
-    // never launch more CTAs than there are batches to hand out
+int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
+    ScanPlan p;
+    int sms = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return fail(4, std::string("scan plan: ") + cudaGetErrorString(e));
+    const size_t head = (size_t)cand_capacity(k) * 8 + 16;
+    const size_t q = (size_t)chunks * q_smem_per_chunk(type);
+    // register-staged kernel
+    p.g = scan_group_width(chunks);
+    p.smem = head + q;
+    {
+        scan_fn fn = pick(type, p.g);
+        e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        int per_sm = 0;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void *)fn, kScanThreads, p.smem);
+        if (e != cudaSuccess) return fail(4, std::string("scan plan: ") + cudaGetErrorString(e));
+        p.grid = std::max(per_sm, 1) * sms;
+    }
+    // TMA-staged kernel
+    const int ld = chunks * 16;
+    p.n_slabs = (ld + kBulkSlabMax - 1) / kBulkSlabMax;
+    p.slab_bytes = (int)round_up((ld + p.n_slabs - 1) / p.n_slabs, 16);
+    p.bulk_g = scan_group_width(p.slab_bytes / 16);
+    p.bulk_smem = ((head + kBulkWarps * kBulkStages * 8 + q + 127) & ~(size_t)127) +
+                  (size_t)kBulkWarps * kBulkStages * 32 * p.slab_bytes;
+    p.bulk_ok = p.bulk_smem <= kSmemLimit;
+    p.bulk_grid = sms;
+    if (p.bulk_ok) {
+        bulk_fn fn = pick_bulk(type, p.bulk_g);
+        e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.bulk_smem);
+        if (e != cudaSuccess) return fail(4, std::string("scan plan (bulk): ") + cudaGetErrorString(e));
+    }
+    *plan = p;
+    return 0;
+}
+
+int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream) {
     const long long batches = (a.n + 31) / 32;
-    if (batches < grid) grid = (int)(batches > 0 ? batches : 1);
-    fn<<<grid, kScanThreads, smem, stream>>>(a);
+    // the TMA-staged kernel needs whole, contiguous rows and enough batches to fill its pipeline
+    const bool bulk = plan.bulk_ok && a.slots == nullptr && batches >= (long long)plan.bulk_grid * kBulkWarps;
+    if (bulk) {
+        bulk_fn fn = pick_bulk(type, plan.bulk_g);
+        fn<<<plan.bulk_grid, kBulkWarps * 32, plan.bulk_smem, stream>>>(a, plan.slab_bytes, plan.n_slabs);
+    } else {
+        scan_fn fn = pick(type, plan.g);
+        int grid = plan.grid;
+        if (batches < grid) grid = (int)(batches > 0 ? batches : 1);  // never more CTAs than batches
+        fn<<<grid, kScanThreads, plan.smem, stream>>>(a);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(e));
     return 0;
 }
+
+int scan_max_grid(const ScanPlan &plan) { return std::max(plan.grid, plan.bulk_grid); }
 
 int merge_launch(const MergeArgs &a, cudaStream_t stream) {
     const size_t smem = (size_t)cand_capacity(a.k) * 8 + 16;

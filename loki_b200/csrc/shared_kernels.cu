@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_scan_shared(const SharedArg
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    cand_select_from_global(buf, a.part, (long long)gridDim.x * a.k);
+    cand_select_from_lists(buf, a.part, (int)gridDim.x);
     const int cnt = buf.ctrl->count;
     for (int i = tid; i < a.k; i += kScanThreads) {
         const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;

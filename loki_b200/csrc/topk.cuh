@@ -16,7 +16,7 @@
 
 namespace lk {
 
-constexpr int kScanThreads = 256;           // threads per scan CTA
+constexpr int kScanThreads = 256;           // most threads any selecting CTA has (sizes the buffer slack)
 constexpr int kScanWarps = kScanThreads / 32;
 constexpr int kMaxK = 2048;                 // largest k one pass selects; larger k runs more passes
 
@@ -43,7 +43,7 @@ struct CandBuf {
     int k;
 };
 
-// Sort keys[0..count) descending, keep the best k, zero the rest, refresh thr.
+// Sort keys[0..count) descending, keep the best k, zero the rest, raise thr.
 // Must be called by all threads of the CTA with `count` stable.
 __device__ inline void cand_prune(const CandBuf &b) {
     const int tid = threadIdx.x, T = blockDim.x;
@@ -70,7 +70,7 @@ __device__ inline void cand_prune(const CandBuf &b) {
     for (int i = keep + tid; i < sz; i += T) b.keys[i] = 0ull;
     if (tid == 0) {
         b.ctrl->count = keep;
-        b.ctrl->thr = (keep == b.k) ? b.keys[b.k - 1] : 0ull;
+        if (keep == b.k && b.keys[b.k - 1] > b.ctrl->thr) b.ctrl->thr = b.keys[b.k - 1];  // only ever rises
     }
     __syncthreads();
 }
@@ -89,26 +89,46 @@ __device__ __forceinline__ void cand_offer_warp(const CandBuf &b, bool pass, uns
     if (pass) b.keys[base + __popc(m & lanemask_lt())] = key;
 }
 
-// Select the best k of a list of keys in global memory (zeros are skipped) into
-// the buffer, sorted descending.  All threads of the CTA call this in lockstep.
-__device__ inline void cand_select_from_global(const CandBuf &b, const unsigned long long *src,
-                                               long long total) {
+// Select the best k out of `lists` ranked lists of k keys each (global memory, zero
+// padded, list l at src[l*k]) into the buffer, sorted descending.  All threads of
+// the CTA call this in lockstep.
+//
+// When there are at least k lists, the k-th largest list head is a lower bound on
+// the k-th best key overall (k lists each hold a key at least that large), so it is
+// used as the starting threshold and nearly every key fails its first compare.
+__device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned long long *src, int lists) {
     const int tid = threadIdx.x, T = blockDim.x;
+    const long long total = (long long)lists * b.k;
     for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
     if (tid == 0) {
         b.ctrl->count = 0;
         b.ctrl->thr = 0ull;
     }
     __syncthreads();
+    if (lists >= b.k && lists <= b.cap) {
+        for (int l = tid; l < lists; l += T) b.keys[l] = __ldcg(src + (size_t)l * b.k);
+        __syncthreads();
+        for (int l = tid; l < lists; l += T) {
+            const unsigned long long h = b.keys[l];
+            int rank = 0;
+            for (int m = 0; m < lists; ++m) rank += (b.keys[m] > h) ? 1 : 0;
+            if (rank == b.k - 1 && h > 0ull) b.ctrl->thr = h - 1ull;  // keys are unique: one writer
+        }
+        __syncthreads();
+        for (int l = tid; l < lists; l += T) b.keys[l] = 0ull;
+        __syncthreads();
+    }
     for (long long base = 0; base < total; base += T) {
-        long long i = base + tid;
-        unsigned long long key = (i < total) ? __ldcg(src + i) : 0ull;
+        const long long i = base + tid;
+        const unsigned long long key = (i < total) ? __ldcg(src + i) : 0ull;
         if (key > *(volatile unsigned long long *)&b.ctrl->thr) {
-            int pos = atomicAdd(&b.ctrl->count, 1);
+            const int pos = atomicAdd(&b.ctrl->count, 1);
             b.keys[pos] = key;
         }
         __syncthreads();
-        if (b.ctrl->count > b.limit) cand_prune(b);  // uniform: count is stable after the barrier
+        const int c = b.ctrl->count;
+        __syncthreads();
+        if (c > b.limit) cand_prune(b);
     }
     cand_prune(b);
 }
