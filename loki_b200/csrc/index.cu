@@ -190,6 +190,8 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
         a.part = (unsigned long long *)idx->part.p;
         a.ticket = idx->d_ticket;
         a.error = (int *)(idx->d_ticket + 1);
+        // consecutive launches may overlap at their edges: each uses its own batch counter
+        a.next_batch = idx->d_ticket + 2 + (idx->scan_launches & 3);
         a.out_keys = res.d_keys() + o;
         a.out_ids = res.d_ids() + o;
         a.out_scores = res.d_scores() + o;

@@ -19,6 +19,7 @@ struct ScanArgs {
     const unsigned long long *bound;  // nullptr, or exclusive upper bound on accepted keys
     unsigned long long *part;   // scratch [grid][k]: per-CTA candidate lists
     unsigned int *ticket;       // scratch: CTAs finished so far (self-resetting)
+    unsigned int *next_batch;   // scratch: next 32-row batch to hand out (TMA-staged kernel; self-resetting)
     int *error;                 // scratch: raised by a CTA whose bounded wait ran out (self-resetting)
     unsigned long long *out_keys;  // [k] ranked keys, zero padded
     long long *out_ids;         // [k] shard_base + slot, -1 padded
@@ -49,6 +50,7 @@ struct ScanPlan {
     int bulk_grid = 1;     // one CTA per SM
     int slab_bytes = 0;    // bytes of each row held per stage
     int n_slabs = 1;       // stages per 32-row batch
+    int fixed_chunks = 0;  // > 0: slab width (in 16-byte chunks) has a compile-time kernel
     size_t bulk_smem = 0;
 };
 int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan);

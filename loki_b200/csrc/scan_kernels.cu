@@ -236,6 +236,25 @@ __device__ __forceinline__ typename TR::acc_t batch_reduce(typename TR::acc_t (&
     return acc[0];
 }
 
+// Fixed-shape variant for the TMA-staged kernel: SC chunks per row slab and the row
+// stride are compile-time, so every shared-memory load has an immediate offset and
+// the whole batch unrolls; q[jj] is the query chunk for this lane's jj-th column.
+template <class TR, int G, int SC>
+__device__ __forceinline__ void slab_accumulate_fixed(typename TR::acc_t (&acc)[G],
+                                                      const typename TR::QChunk (&q)[SC / G],
+                                                      const unsigned char *stage, int lane) {
+    constexpr int NJ = SC / G, W = SC * 16;
+    const unsigned char *base = stage + (size_t)(lane / G) * G * W + (size_t)(lane % G) * 16;
+#pragma unroll
+    for (int t = 0; t < G; ++t) {
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) {
+            const int4 v = *reinterpret_cast<const int4 *>(base + t * W + jj * G * 16);
+            TR::dot(acc[t], v, q[jj]);
+        }
+    }
+}
+
 // Shared tail of both scan kernels: publish this CTA's list; the last CTA to arrive
 // merges all lists and writes the result.
 template <int TYPE>
@@ -263,6 +282,7 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
         const bool bad = a.error != nullptr && *(volatile int *)a.error != 0;
         *a.out_count = bad ? -1 : cnt;
         if (bad) *a.error = 0;
+        if (a.next_batch != nullptr) *a.next_batch = 0u;
         *a.ticket = 0u;
     }
 }
@@ -362,7 +382,13 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const ScanArgs a) {
 // buffer.  Bytes in flight per SM = warps x (kStages-1..kStages) x tile, independent
 // of register pressure, which is what it takes to keep HBM3e busy from 148 SMs.
 // ---------------------------------------------------------------------------
-constexpr int kBulkStages = 2;
+#ifndef LK_BULK_STAGES
+#define LK_BULK_STAGES 2
+#endif
+#ifndef LK_BULK_WARPS
+#define LK_BULK_WARPS 4
+#endif
+constexpr int kBulkStages = LK_BULK_STAGES;
 constexpr unsigned kBulkSpinLimit = 1u << 22;  // bounded wait on a tile (each try blocks briefly in hardware)
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -392,9 +418,28 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned b
                  : "memory");
 }
 
-template <class TR, int TYPE, int G, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, int slab_bytes, int n_slabs) {
+// SC > 0 fixes the slab width at compile time (SC 16-byte chunks, G must divide SC);
+// SC == 0 takes it from slab_bytes.  QREG keeps the query in registers (one slab per row).
+#ifdef LK_TIMELINE
+__device__ unsigned long long *g_timeline;  // [grid][8] nanosecond stamps (tuning builds only)
+__device__ __forceinline__ void tl_stamp(int i) {
+    if (threadIdx.x == 0 && g_timeline) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_timeline[blockIdx.x * 8 + i] = t;
+    }
+}
+#define LK_TL(i) tl_stamp(i)
+#else
+#define LK_TL(i)
+#endif
+
+template <class TR, int TYPE, int G, int WARPS, int SC, bool QREG>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, int slab_bytes_rt, int n_slabs_rt) {
+    const int slab_bytes = SC > 0 ? SC * 16 : slab_bytes_rt;
+    const int n_slabs = QREG ? 1 : n_slabs_rt;
     extern __shared__ __align__(128) unsigned char smem[];
+    LK_TL(0);
     constexpr int R = (G < 4) ? G : 4;  // shared-memory latency is short: few rows in flight suffice
     constexpr int T = WARPS * 32;
     using acc_t = typename TR::acc_t;
@@ -413,36 +458,63 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, i
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid; i < buf.cap; i += T) buf.keys[i] = 0ull;
+    // Let the next launch on the stream begin as soon as SMs fall free: consecutive
+    // queries are independent until they publish (see the wait before the publish).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
-        buf.ctrl->count = 0;
-        buf.ctrl->n_done = 0;
-        buf.ctrl->thr = 0ull;
         for (int i = 0; i < WARPS * kBulkStages; ++i) mbar_init(&bars[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    TR::stage_query(qs, a.query, a.chunks);
-    const unsigned long long bound = a.bound ? __ldcg(a.bound) : ~0ull;
-    __syncthreads();
+    __syncthreads();  // barriers are initialised: the first copies can go out before anything else
 
     const long long n_batches = (a.n + 31) >> 5;
-    const long long b_lo = n_batches * blockIdx.x / gridDim.x;
-    const long long b_hi = n_batches * (blockIdx.x + 1) / gridDim.x;
     unsigned char *my_stages = stages + (size_t)warp * kBulkStages * stage_bytes;
     unsigned long long *my_bars = bars + warp * kBulkStages;
 
-    // Item m of this warp = (batch b_lo + warp + (m / n_slabs) * WARPS, slab m % n_slabs); it
-    // lives in stage m % kBulkStages.  A slab is a column range of slab_bytes of each row
-    // (the last one may be narrower); rows are packed slab_w bytes apart in the stage.
+    // Work is handed out dynamically: a warp takes the next 32-row batch from a global
+    // counter whenever one of its stages falls free, so SMs that get more bandwidth
+    // simply take more batches and all SMs finish together.  A batch is loaded in
+    // n_slabs items (column ranges of slab_bytes of each row; the last may be narrower;
+    // rows sit slab-width bytes apart in the stage); item m of a warp lives in stage
+    // m % kBulkStages and items are consumed in the order they were issued.
     auto slab_width = [&](int sl) -> int { return min(slab_bytes, (int)a.ld - sl * slab_bytes); };
-    auto issue = [&](long long m) {  // called by the whole warp
-        const long long b = b_lo + warp + (m / n_slabs) * WARPS;
-        if (b >= b_hi) return;
-        const int sl = (int)(m % n_slabs);
-        const long long row0 = b << 5;
+    long long stage_batch[kBulkStages];  // batch held by each stage, -1 = none
+#pragma unroll
+    for (int s = 0; s < kBulkStages; ++s) stage_batch[s] = -1;
+    long long iss_batch = -1;  // batch whose slabs are being issued
+    int iss_slab = 0;
+    bool exhausted = false;
+    // The first kBulkStages batches of every warp are fixed (no round trip to the
+    // counter before the first copy); the counter hands out the batches after those.
+    const long long static_base = ((long long)blockIdx.x * WARPS + warp) * kBulkStages;
+    const long long first_dynamic = (long long)gridDim.x * WARPS * kBulkStages;
+    int static_used = 0;
+    auto issue = [&](int s) {  // called by the whole warp: fill stage s with the next item
+        long long bnew = -1;
+        if (iss_slab == 0) {
+            if (!exhausted) {
+                long long t;
+                if (static_used < kBulkStages) {
+                    t = static_base + static_used++;
+                } else {
+                    unsigned d = 0;
+                    if (lane == 0) d = atomicAdd(a.next_batch, 1u);
+                    t = first_dynamic + (long long)__shfl_sync(0xffffffffu, d, 0);
+                }
+                if (t < n_batches) iss_batch = t; else exhausted = true;
+            }
+            if (exhausted) iss_batch = -1;
+        }
+        bnew = iss_batch;
+#pragma unroll
+        for (int i = 0; i < kBulkStages; ++i)
+            if (i == s) stage_batch[i] = bnew;
+        if (bnew < 0) return;
+        const int sl = iss_slab;
+        iss_slab = (iss_slab + 1 == n_slabs) ? 0 : iss_slab + 1;
+        const long long row0 = bnew << 5;
         const int rows = (int)min(32ll, a.n - row0);
         const int w = slab_width(sl);
-        const int s = (int)(m % kBulkStages);
         unsigned char *dst = my_stages + (size_t)s * stage_bytes;
         if (lane == 0) mbar_expect_tx(&my_bars[s], (unsigned)(rows * w));
         __syncwarp();
@@ -453,21 +525,48 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, i
                       (unsigned)w, &my_bars[s]);
         }
     };
-    for (int m = 0; m < kBulkStages; ++m) issue(m);
+#pragma unroll
+    for (int s = 0; s < kBulkStages; ++s) issue(s);
+    LK_TL(1);
+
+    // the rest of the prologue runs while the first copies are in flight
+    for (int i = tid; i < buf.cap; i += T) buf.keys[i] = 0ull;
+    if (tid == 0) {
+        buf.ctrl->count = 0;
+        buf.ctrl->n_done = 0;
+        buf.ctrl->thr = 0ull;
+    }
+    TR::stage_query(qs, a.query, a.chunks);
+    unsigned long long bound = ~0ull;
+    if (a.bound != nullptr) {  // a later pass of a large-k search: its bound is the previous pass's output
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        bound = __ldcg(a.bound);
+    }
+    __syncthreads();
+
+    constexpr int NJ = SC > 0 ? SC / G : 1;
+    typename TR::QChunk qreg[NJ];
+    if (QREG) {
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) qreg[jj] = TR::load_q(qs, (lane % G) + jj * G, a.chunks);
+    }
 
     long long m = 0;
     bool counted = false, failed = false;
     acc_t acc[G];
     for (;;) {
-        const long long b = b_lo + warp + (m / n_slabs) * WARPS;
+        const int s = (int)(m % kBulkStages);
         const int sl = (int)(m % n_slabs);
-        const bool work = b < b_hi && !failed;
+        long long b = -1;
+#pragma unroll
+        for (int i = 0; i < kBulkStages; ++i)
+            if (i == s) b = stage_batch[i];
+        const bool work = b >= 0 && !failed;
         int seen = 0;
         if (lane == 0) seen = *(volatile int *)&buf.ctrl->count;
         seen = __shfl_sync(0xffffffffu, seen, 0);
         // the buffer is only looked at between batches: a batch in progress always finishes
         if (work && (sl != 0 || seen <= buf.limit)) {
-            const int s = (int)(m % kBulkStages);
             const unsigned parity = (unsigned)((m / kBulkStages) & 1);
             // bounded wait for the data; on expiry flag the error and stop taking work
             unsigned spins = 0;
@@ -478,6 +577,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, i
                 failed = true;
                 continue;
             }
+            if (m == 0) LK_TL(2);
             const long long row0 = b << 5;
             const int rows = (int)min(32ll, a.n - row0);
             const int w = slab_width(sl);
@@ -486,14 +586,27 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, i
 #pragma unroll
                 for (int t = 0; t < G; ++t) acc[t] = (acc_t)0;
             }
-            batch_accumulate<TR, G, R, LoadShared>(
-                acc, qs, a.chunks, sl * (slab_bytes >> 4), w >> 4, lane,
-                [&](int i) -> const unsigned char * { return stage + (size_t)(i < rows ? i : 0) * w; },
-                [&](int i) -> bool { return i < rows; });
+            // Rows past the end of a short last batch hold stale bytes: they are scored like any
+            // other (shared memory is always readable) and dropped by `valid` below.
+            if (SC > 0) {
+                if (QREG) {
+                    slab_accumulate_fixed<TR, G, (SC > 0 ? SC : G)>(acc, qreg, stage, lane);
+                } else {
+                    typename TR::QChunk q[NJ];
+#pragma unroll
+                    for (int jj = 0; jj < NJ; ++jj) q[jj] = TR::load_q(qs, sl * SC + (lane % G) + jj * G, a.chunks);
+                    slab_accumulate_fixed<TR, G, (SC > 0 ? SC : G)>(acc, q, stage, lane);
+                }
+            } else {
+                batch_accumulate<TR, G, R, LoadShared>(
+                    acc, qs, a.chunks, sl * (slab_bytes >> 4), w >> 4, lane,
+                    [&](int i) -> const unsigned char * { return stage + (size_t)i * w; },
+                    [&](int) -> bool { return true; });
+            }
             // every lane has its part of the stage in registers (the accumulators depend on
-            // it): the stage is free, refill it with this warp's item m + kBulkStages
+            // it): the stage is free, refill it with this warp's next item
             __syncwarp();
-            issue(m + kBulkStages);
+            issue(s);
             ++m;
             if (sl != n_slabs - 1) continue;
             const acc_t total = batch_reduce<TR, G>(acc, lane);
@@ -505,19 +618,30 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, i
             cand_offer_warp(buf, valid && key > thr && key < bound, key);
             continue;
         }
+        if (!work) LK_TL(3);
         if (cand_rendezvous(buf, work, counted, lane, WARPS)) break;
     }
+    LK_TL(4);
     // A warp that gave up may still have copies in flight into its stages: wait for
     // them (bounded) before the CTA's shared memory is released.
     if (failed) {
         for (long long mm = m; mm < m + kBulkStages; ++mm) {
-            if (b_lo + warp + (mm / n_slabs) * WARPS >= b_hi) break;
+            long long b = -1;
+#pragma unroll
+            for (int i = 0; i < kBulkStages; ++i)
+                if (i == (int)(mm % kBulkStages)) b = stage_batch[i];
+            if (b < 0) continue;
             unsigned spins = 0;
             while (!mbar_try_wait(&my_bars[mm % kBulkStages], (unsigned)((mm / kBulkStages) & 1)) &&
                    ++spins < kBulkSpinLimit) {}
         }
     }
+    // Everything up to here touched only this launch's own state.  The scratch shared
+    // with the previous launch on the stream (per-CTA lists, ticket) is next: wait until
+    // that launch has completely finished.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     publish_and_finish<TYPE>(a, buf, &s_last);
+    LK_TL(5);
 }
 
 // ---------------------------------------------------------------------------
@@ -615,12 +739,15 @@ static int q_smem_per_chunk(int type) {
     return (type == SCAN_I8) ? TraitsI8::kQBytes : (type == SCAN_F32 ? TraitsF32::kQBytes : TraitsF16::kQBytes);
 }
 
-constexpr int kBulkWarps = 4;
+constexpr int kBulkWarps = LK_BULK_WARPS;
 constexpr int kBulkSlabMax = 768;               // bytes of one row kept per stage: 32 rows x 768 B = 24 KB
 constexpr size_t kSmemLimit = 227 * 1024;
 
 typedef void (*scan_fn)(const ScanArgs);
 typedef void (*bulk_fn)(const ScanArgs, int, int);
+
+// slab shapes with a compile-time kernel: 48 chunks (768 B) and 32 chunks (512 B)
+static int bulk_fixed_chunks(int ld) { return (ld % 768 == 0) ? 48 : ((ld % 512 == 0) ? 32 : 0); }
 
 template <class TR, int TYPE>
 static scan_fn pick_g(int g) {
@@ -641,21 +768,24 @@ static scan_fn pick(int type, int g) {
     }
 }
 template <class TR, int TYPE>
-static bulk_fn pick_bulk_g(int g) {
+static bulk_fn pick_bulk_g(int g, int sc, bool qreg) {
+    if (sc == 48) return qreg ? k_scan_bulk<TR, TYPE, 16, kBulkWarps, 48, true> : k_scan_bulk<TR, TYPE, 16, kBulkWarps, 48, false>;
+    if (sc == 32) return qreg ? k_scan_bulk<TR, TYPE, 32, kBulkWarps, 32, true> : k_scan_bulk<TR, TYPE, 32, kBulkWarps, 32, false>;
     switch (g) {
-        case 1: return k_scan_bulk<TR, TYPE, 1, kBulkWarps>;
-        case 2: return k_scan_bulk<TR, TYPE, 2, kBulkWarps>;
-        case 4: return k_scan_bulk<TR, TYPE, 4, kBulkWarps>;
-        case 8: return k_scan_bulk<TR, TYPE, 8, kBulkWarps>;
-        case 16: return k_scan_bulk<TR, TYPE, 16, kBulkWarps>;
-        default: return k_scan_bulk<TR, TYPE, 32, kBulkWarps>;
+        case 1: return k_scan_bulk<TR, TYPE, 1, kBulkWarps, 0, false>;
+        case 2: return k_scan_bulk<TR, TYPE, 2, kBulkWarps, 0, false>;
+        case 4: return k_scan_bulk<TR, TYPE, 4, kBulkWarps, 0, false>;
+        case 8: return k_scan_bulk<TR, TYPE, 8, kBulkWarps, 0, false>;
+        case 16: return k_scan_bulk<TR, TYPE, 16, kBulkWarps, 0, false>;
+        default: return k_scan_bulk<TR, TYPE, 32, kBulkWarps, 0, false>;
     }
 }
-static bulk_fn pick_bulk(int type, int g) {
+static bulk_fn pick_bulk(int type, const ScanPlan &p) {
+    const bool qreg = p.fixed_chunks > 0 && p.n_slabs == 1;
     switch (type) {
-        case SCAN_I8: return pick_bulk_g<TraitsI8, SCAN_I8>(g);
-        case SCAN_F32: return pick_bulk_g<TraitsF32, SCAN_F32>(g);
-        default: return pick_bulk_g<TraitsF16, SCAN_F16>(g);
+        case SCAN_I8: return pick_bulk_g<TraitsI8, SCAN_I8>(p.bulk_g, p.fixed_chunks, qreg);
+        case SCAN_F32: return pick_bulk_g<TraitsF32, SCAN_F32>(p.bulk_g, p.fixed_chunks, qreg);
+        default: return pick_bulk_g<TraitsF16, SCAN_F16>(p.bulk_g, p.fixed_chunks, qreg);
     }
 }
 
@@ -679,15 +809,21 @@ int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
     }
     // TMA-staged kernel
     const int ld = chunks * 16;
-    p.n_slabs = (ld + kBulkSlabMax - 1) / kBulkSlabMax;
-    p.slab_bytes = (int)round_up((ld + p.n_slabs - 1) / p.n_slabs, 16);
+    p.fixed_chunks = bulk_fixed_chunks(ld);
+    if (p.fixed_chunks > 0) {
+        p.slab_bytes = p.fixed_chunks * 16;
+        p.n_slabs = ld / p.slab_bytes;
+    } else {
+        p.n_slabs = (ld + kBulkSlabMax - 1) / kBulkSlabMax;
+        p.slab_bytes = (int)round_up((ld + p.n_slabs - 1) / p.n_slabs, 16);
+    }
     p.bulk_g = scan_group_width(p.slab_bytes / 16);
     p.bulk_smem = ((head + kBulkWarps * kBulkStages * 8 + q + 127) & ~(size_t)127) +
                   (size_t)kBulkWarps * kBulkStages * 32 * p.slab_bytes;
     p.bulk_ok = p.bulk_smem <= kSmemLimit;
     p.bulk_grid = sms;
     if (p.bulk_ok) {
-        bulk_fn fn = pick_bulk(type, p.bulk_g);
+        bulk_fn fn = pick_bulk(type, p);
         e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.bulk_smem);
         if (e != cudaSuccess) return fail(4, std::string("scan plan (bulk): ") + cudaGetErrorString(e));
     }
@@ -700,8 +836,19 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
     // the TMA-staged kernel needs whole, contiguous rows and enough batches to fill its pipeline
     const bool bulk = plan.bulk_ok && a.slots == nullptr && batches >= (long long)plan.bulk_grid * kBulkWarps;
     if (bulk) {
-        bulk_fn fn = pick_bulk(type, plan.bulk_g);
-        fn<<<plan.bulk_grid, kBulkWarps * 32, plan.bulk_smem, stream>>>(a, plan.slab_bytes, plan.n_slabs);
+        bulk_fn fn = pick_bulk(type, plan);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)plan.bulk_grid);
+        cfg.blockDim = dim3(kBulkWarps * 32);
+        cfg.dynamicSmemBytes = plan.bulk_smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t le = cudaLaunchKernelEx(&cfg, fn, a, plan.slab_bytes, plan.n_slabs);
+        if (le != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(le));
     } else {
         scan_fn fn = pick(type, plan.g);
         int grid = plan.grid;

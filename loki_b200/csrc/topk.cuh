@@ -93,42 +93,81 @@ __device__ __forceinline__ void cand_offer_warp(const CandBuf &b, bool pass, uns
 // padded, list l at src[l*k]) into the buffer, sorted descending.  All threads of
 // the CTA call this in lockstep.
 //
-// When there are at least k lists, the k-th largest list head is a lower bound on
-// the k-th best key overall (k lists each hold a key at least that large), so it is
-// used as the starting threshold and nearly every key fails its first compare.
+// Starting threshold.  Let p = ceil(k / lists) - 1 and j = ceil(k / (p+1)): the j-th
+// largest of the lists' entries at position p has at least j*(p+1) >= k keys at or
+// above it (p+1 from each of j lists), so it is a lower bound on the k-th best key
+// overall and nearly every key fails its first compare against it.
+//
+// Keys are fetched kSelectUnroll per thread at a time with independent loads (one
+// memory latency per round instead of one per key).  Should a round offer more keys
+// than the buffer has room for, the buffer is pruned and the same registers are
+// offered again, so nothing is ever dropped.
+constexpr int kSelectUnroll = 16;
+
 __device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned long long *src, int lists) {
     const int tid = threadIdx.x, T = blockDim.x;
     const long long total = (long long)lists * b.k;
+    __shared__ int s_overflow;
     for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
     if (tid == 0) {
         b.ctrl->count = 0;
         b.ctrl->thr = 0ull;
+        s_overflow = 0;
     }
     __syncthreads();
-    if (lists >= b.k && lists <= b.cap) {
-        for (int l = tid; l < lists; l += T) b.keys[l] = __ldcg(src + (size_t)l * b.k);
+    if (lists <= b.cap) {
+        const int p = (b.k + lists - 1) / lists - 1;
+        const int j = (b.k + p) / (p + 1);
+        for (int l = tid; l < lists; l += T) b.keys[l] = __ldcg(src + (size_t)l * b.k + p);
         __syncthreads();
         for (int l = tid; l < lists; l += T) {
             const unsigned long long h = b.keys[l];
             int rank = 0;
             for (int m = 0; m < lists; ++m) rank += (b.keys[m] > h) ? 1 : 0;
-            if (rank == b.k - 1 && h > 0ull) b.ctrl->thr = h - 1ull;  // keys are unique: one writer
+            if (rank == j - 1 && h > 0ull) b.ctrl->thr = h - 1ull;  // keys are unique: one writer
         }
         __syncthreads();
         for (int l = tid; l < lists; l += T) b.keys[l] = 0ull;
         __syncthreads();
     }
-    for (long long base = 0; base < total; base += T) {
-        const long long i = base + tid;
-        const unsigned long long key = (i < total) ? __ldcg(src + i) : 0ull;
-        if (key > *(volatile unsigned long long *)&b.ctrl->thr) {
-            const int pos = atomicAdd(&b.ctrl->count, 1);
-            b.keys[pos] = key;
+    for (long long base = 0; base < total; base += (long long)T * kSelectUnroll) {
+        unsigned long long key[kSelectUnroll];
+#pragma unroll
+        for (int u = 0; u < kSelectUnroll; ++u) {
+            const long long i = base + (long long)u * T + tid;
+            key[u] = (i < total) ? __ldcg(src + i) : 0ull;
         }
-        __syncthreads();
-        const int c = b.ctrl->count;
-        __syncthreads();
-        if (c > b.limit) cand_prune(b);
+        for (;;) {
+            const unsigned long long thr = *(volatile unsigned long long *)&b.ctrl->thr;
+#pragma unroll
+            for (int u = 0; u < kSelectUnroll; ++u) {
+                if (key[u] > thr) {
+                    const int pos = atomicAdd(&b.ctrl->count, 1);
+                    if (pos < b.cap) {
+                        b.keys[pos] = key[u];
+                        key[u] = 0ull;
+                    } else {
+                        s_overflow = 1;  // keep the key in its register for the next attempt
+                    }
+                } else {
+                    key[u] = 0ull;
+                }
+            }
+            __syncthreads();
+            const int c = b.ctrl->count;
+            const int ov = s_overflow;
+            __syncthreads();
+            if (ov == 0) {
+                if (c > b.limit) cand_prune(b);
+                break;
+            }
+            if (tid == 0) {
+                b.ctrl->count = b.cap;  // every slot below cap was written
+                s_overflow = 0;
+            }
+            __syncthreads();
+            cand_prune(b);
+        }
     }
     cand_prune(b);
 }
