@@ -188,6 +188,36 @@ LK_API int lk_hamming_scan(const uint64_t *hashes, int64_t n, uint64_t query, in
                            int device, uint32_t *out_ids, int32_t *out_dist, int64_t cap,
                            int64_t *count);
 
+/* ---- scan without any allocation (no counterpart in the reference) ---------- */
+
+/* For callers that are not allowed to allocate device memory while they run: a server
+ * whose GPU budget is handed out once at start-up, a request path that cannot afford
+ * the device-wide stall of cudaMalloc / cudaFree, a plug-in inside another framework's
+ * memory arena.  One int8 top-k scan (same kernel, same ranking as lk_search on an
+ * LK_I8 index); every buffer is a DEVICE pointer owned by the caller, and the kernel's
+ * scratch is a fixed array inside the library image, LK_PREALLOC_SCRATCH_BYTES per GPU
+ * that loads the library, held until the process exits.  The call makes no cudaMalloc,
+ * cudaFree or other allocating call; it enqueues on `stream` (a cudaStream_t, NULL =
+ * default stream) and returns without waiting.
+ *   d_codes   n rows of int8 codes, ld bytes apart (ld a multiple of 16, padding zero),
+ *             16-byte aligned: the layout lk_index_read_rows describes, kept on device
+ *   d_scales  n per-row float scales (score = int dot * query_scale * row scale)
+ *   d_query   ld bytes: the query's int8 codes, zero padded; query_scale its scale
+ *   k         1..LK_PREALLOC_MAX_K; larger k is refused with LK_ERANGE
+ *   outputs   k ids (row numbers, -1 padded), k float scores, k raw int32 dots (may be
+ *             NULL), one count (-1 if a bounded wait inside the kernel ran out)
+ * The first call on a device looks up the scratch array's address; make that call
+ * once per device before starting any stream capture.  All calls on a device share the
+ * one array, which keeps the previous call's contents (the call clears the few words
+ * that must start at zero): calls that overlap on the GPU, e.g. on two streams, race. */
+#define LK_PREALLOC_MAX_K 128
+#define LK_PREALLOC_MAX_CTAS 1024
+#define LK_PREALLOC_SCRATCH_BYTES (256 + LK_PREALLOC_MAX_K * 8 + LK_PREALLOC_MAX_CTAS * LK_PREALLOC_MAX_K * 8)
+LK_API int lk_scan_i8_prealloc(int device, const int8_t *d_codes, int64_t n, int dim, int64_t ld,
+                               const float *d_scales, const int8_t *d_query, float query_scale, int k,
+                               int64_t *d_out_ids, float *d_out_scores, int32_t *d_out_iscores,
+                               int32_t *d_out_count, void *stream);
+
 /* ---- statistics ----------------------------------------------------------- */
 
 typedef struct {

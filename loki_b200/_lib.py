@@ -90,6 +90,8 @@ _sig("lk_index_set_shard_base", _int, _vp, _i64)
 _sig("lk_hamming_pairs", _int, _vp, _i64, _int, _int, _int, _int, _vp, _i64, C.POINTER(_i64))
 _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64, C.POINTER(_i64))
 _sig("lk_stats", _int, _vp, C.POINTER(lk_stats_t))
+_sig("lk_scan_i8_prealloc", _int, _int, _vp, _i64, _int, _i64, _vp, _vp, C.c_float, _int, _vp, _vp, _vp, _vp, _vp)
+LK_PREALLOC_MAX_K = 128
 
 
 def check(status: int):
