@@ -1,0 +1,88 @@
+"""GPU, 2 ranks (one process per GPU): the sharded search over NCCL gives the same
+result as one index holding every row.  Skipped when fewer than 2 GPUs are visible."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys
+sys.path.insert(0, os.environ["LK_ROOT"])
+import numpy as np
+import torch
+import torch.distributed as dist
+from loki_b200 import _lib as lk
+from loki_b200 import sharding as S
+from tests.synth import clustered_rows, gaussian_rows
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+n, dim, k = 20011, 768, 50
+rows = clustered_rows(n, dim, 5)
+queries = gaussian_rows(5, dim, 6)
+uid = [lk.Comm.unique_id() if rank == 0 else None]
+dist.broadcast_object_list(uid, src=0)
+comm = lk.Comm(world, rank, rank, uid[0])
+out = {}
+for name, store in (("i8", lk.LK_I8), ("f32", lk.LK_F32)):
+    base, cnt = S.shard_bounds(n, world)[rank]
+    idx = lk.DeviceIndex(dim, store, device=rank)
+    idx.append(rows[base:base + cnt])
+    idx.attach_comm(comm, base)
+    ids, scores, iscores, counts = idx.search(queries, k)
+    rq = idx.queries(queries)
+    rq.enqueue(0, 5, k)
+    ids2, scores2, iscores2, counts2 = rq.fetch(0, 5, k)
+    assert np.array_equal(ids, ids2) and np.array_equal(scores, scores2) and np.array_equal(iscores, iscores2)
+    out[name + "_ids"], out[name + "_scores"], out[name + "_iscores"] = ids, scores, iscores
+    rq.close(); idx.close()
+np.savez(os.path.join(os.environ["LK_OUT"], f"rank{rank}.npz"), **out)
+dist.barrier()
+comm.close()
+dist.destroy_process_group()
+'''
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_sharded_search_over_nccl_equals_single_index(lk, tmp_path):
+    if lk.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from tests.synth import clustered_rows, gaussian_rows
+    world = 2
+    port = _free_port()
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), LK_ROOT=ROOT, LK_OUT=str(tmp_path), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o[-3000:]
+    n, dim, k = 20011, 768, 50
+    rows = clustered_rows(n, dim, 5)
+    queries = gaussian_rows(5, dim, 6)
+    got = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    for name, store in (("i8", lk.LK_I8), ("f32", lk.LK_F32)):
+        idx = lk.DeviceIndex(dim, store)
+        idx.append(rows)
+        ids, scores, iscores, _ = idx.search(queries, k)
+        for g in got:
+            assert np.array_equal(g[name + "_ids"], ids), name
+            assert np.array_equal(g[name + "_scores"], scores), name
+            assert np.array_equal(g[name + "_iscores"], iscores), name
