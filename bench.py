@@ -198,6 +198,10 @@ def run_ours(args):
         uid = [lk.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         comm = lk.Comm(world, rank, local, uid[0])
+        if not args.nccl_merge:  # exchange the per-shard top-k inside the scan kernel, over peer memory
+            handles = [None] * world
+            dist.all_gather_object(handles, comm.peer_export())
+            comm.peer_attach(handles)
         idx.attach_comm(comm, rank * ROWS_PER_GPU)
 
     K, W = args.steps, args.warmup
@@ -265,11 +269,14 @@ def run_ours(args):
                        "rows_per_gpu": ROWS_PER_GPU, "global_rows": ROWS_PER_GPU * world, "dim": DIM, "k": TOPK,
                        "global_queries_per_s": K / (ms * 1e-3),
                        "l2": "shard is 768 MB, larger than the 126 MB L2: every step streams from HBM",
-                       "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-10 + merge kernel per query"},
+                       "merge": "none" if world == 1 else (
+                           "NCCL all-gather of per-shard top-10 + merge kernel per query" if args.nccl_merge else
+                           "inside the scan kernel: each shard's top-10 stored into every rank's inbox over NVLink "
+                           "(peer memory), merged by the last CTA")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "traffic": None,
                          "note": "achieved = rows x 768 B / (timed region / K): launch gaps"
-                                 + (", all-gather and merge" if world > 1 else "") + " are inside the denominator"},
+                                 + (", exchange and merge" if world > 1 else "") + " are inside the denominator"},
             "e2e": {"value": world * E / e2e_s, "unit": "queries/s", "steps": E,
                     "h2d_bytes_per_step": DIM, "d2h_bytes_per_step": (TOPK * 16 + 4 + 15) // 16 * 16,
                     "global_queries_per_s": E / e2e_s, "ms_per_query": e2e_s / E * 1e3},
@@ -295,6 +302,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--nccl-merge", action="store_true",
+                    help="N>1: merge through ncclAllGather + a merge kernel instead of the in-kernel peer exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

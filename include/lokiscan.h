@@ -171,6 +171,17 @@ LK_API int lk_index_sync(lk_index *idx);
 LK_API int lk_comm_unique_id(void *out128);
 LK_API int lk_comm_create(int world, int rank, int device, const void *id128, lk_comm **out);
 LK_API int lk_comm_destroy(lk_comm *c);
+/* Optional fast path for the GPUs of one box: instead of an NCCL all-gather per search,
+ * the scan kernel itself stores each shard's k results into every rank's inbox over
+ * NVLink (peer memory) and merges as soon as all have landed.  Every rank calls
+ * lk_comm_peer_export, the caller passes the LK_PEER_HANDLE_BYTES of each rank to all
+ * ranks (rank order), every rank calls lk_comm_peer_attach, then lk_index_attach_comm.
+ * One process per GPU (CUDA IPC).  Used for k <= 128; larger k takes the NCCL path.
+ * One sharded search at a time per communicator; a rank that does not deliver within
+ * 2 s makes the others return LK_ETIMEOUT. */
+#define LK_PEER_HANDLE_BYTES 64
+LK_API int lk_comm_peer_export(lk_comm *c, void *out_handle);
+LK_API int lk_comm_peer_attach(lk_comm *c, const void *handles /* world x LK_PEER_HANDLE_BYTES */);
 /* This index holds global rows [shard_base, shard_base+len). */
 LK_API int lk_index_attach_comm(lk_index *idx, lk_comm *c, int64_t shard_base);
 LK_API int lk_index_set_shard_base(lk_index *idx, int64_t shard_base);

@@ -85,6 +85,8 @@ _sig("lk_index_sync", _int, _vp)
 _sig("lk_comm_unique_id", _int, _vp)
 _sig("lk_comm_create", _int, _int, _int, _int, _vp, C.POINTER(_vp))
 _sig("lk_comm_destroy", _int, _vp)
+_sig("lk_comm_peer_export", _int, _vp, _vp)
+_sig("lk_comm_peer_attach", _int, _vp, _vp)
 _sig("lk_index_attach_comm", _int, _vp, _vp, _i64)
 _sig("lk_index_set_shard_base", _int, _vp, _i64)
 _sig("lk_hamming_pairs", _int, _vp, _i64, _int, _int, _int, _int, _vp, _i64, C.POINTER(_i64))
@@ -294,6 +296,18 @@ class Comm:
         buf = C.create_string_buffer(bytes(unique_id), 128)
         check(lib.lk_comm_create(int(world), int(rank), int(device), buf, C.byref(h)))
         self._h, self.world, self.rank = h, world, rank
+
+    def peer_export(self) -> bytes:
+        """This rank's inbox handle (64 bytes) for the in-kernel exchange over peer memory."""
+        buf = C.create_string_buffer(64)
+        check(lib.lk_comm_peer_export(self._h, buf))
+        return buf.raw
+
+    def peer_attach(self, handles):
+        """handles: the 64-byte handle of every rank, in rank order."""
+        blob = b"".join(bytes(h) for h in handles)
+        assert len(blob) == 64 * self.world
+        check(lib.lk_comm_peer_attach(self._h, C.create_string_buffer(blob, len(blob))))
 
     def close(self):
         if getattr(self, "_h", None):

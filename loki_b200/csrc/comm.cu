@@ -74,6 +74,12 @@ struct lk_comm {
     ncclComm_t comm = nullptr;
     long long *d_bases = nullptr;  // [world] shard base of every rank (device)
     bool bases_valid = false;
+    // direct exchange over peer memory (optional, see lk_comm_peer_export / _attach)
+    PeerInbox *inbox = nullptr;               // this rank's inbox (cudaMalloc)
+    PeerInbox *peer_inbox[kPeerMaxWorld] = {};  // every rank's inbox as mapped here
+    PeerTable *d_table = nullptr;             // device copy handed to the kernels
+    bool peer_ready = false;
+    unsigned int seq = 0;                     // sharded queries issued so far (same on every rank)
 };
 
 namespace lk {
@@ -112,6 +118,11 @@ int comm_gather_merge(lk_comm *c, lk_index *idx, const ResultArena &res, int q_f
     idx->aux_launches++;
     return 0;
 }
+
+const PeerTable *comm_peer_table(lk_comm *c, int k) {
+    return (c && c->peer_ready && c->d_table && k <= kPeerMaxK) ? c->d_table : nullptr;
+}
+unsigned int comm_next_seq(lk_comm *c) { return c->seq++; }
 
 }  // namespace lk
 
@@ -155,10 +166,53 @@ int lk_comm_create(int world, int rank, int device, const void *id128, lk_comm *
     return LK_OK;
 }
 
+int lk_comm_peer_export(lk_comm *c, void *out64) {
+    if (!c || !out64) return fail(LK_EINVAL, "lk_comm_peer_export: bad argument");
+    if (c->world > kPeerMaxWorld) return fail(LK_ERANGE, "lk_comm_peer_export: more than 16 ranks");
+    LK_CUDA(cudaSetDevice(c->device));
+    if (!c->inbox) {
+        LK_CUDA(cudaMalloc((void **)&c->inbox, sizeof(PeerInbox)));
+        LK_CUDA(cudaMemset(c->inbox, 0, sizeof(PeerInbox)));
+    }
+    cudaIpcMemHandle_t h;
+    LK_CUDA(cudaIpcGetMemHandle(&h, c->inbox));
+    static_assert(sizeof(h) == LK_PEER_HANDLE_BYTES, "CUDA IPC handle size");
+    memcpy(out64, &h, sizeof(h));
+    return LK_OK;
+}
+
+int lk_comm_peer_attach(lk_comm *c, const void *handles) {
+    if (!c || !handles) return fail(LK_EINVAL, "lk_comm_peer_attach: bad argument");
+    if (!c->inbox) return fail(LK_EINVAL, "lk_comm_peer_attach: call lk_comm_peer_export first");
+    LK_CUDA(cudaSetDevice(c->device));
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) {
+            c->peer_inbox[r] = c->inbox;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)r * LK_PEER_HANDLE_BYTES, sizeof(h));
+        void *p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(LK_ECUDA, std::string("cudaIpcOpenMemHandle(rank ") + std::to_string(r) + "): " + cudaGetErrorString(e));
+        }
+        c->peer_inbox[r] = static_cast<PeerInbox *>(p);
+    }
+    if (!c->d_table) LK_CUDA(cudaMalloc((void **)&c->d_table, sizeof(PeerTable)));
+    c->peer_ready = true;
+    return LK_OK;
+}
+
 int lk_comm_destroy(lk_comm *c) {
     if (!c) return LK_OK;
     NcclApi *api = nccl_api();
     cudaSetDevice(c->device);
+    for (int r = 0; r < c->world && r < kPeerMaxWorld; ++r)
+        if (r != c->rank && c->peer_inbox[r]) cudaIpcCloseMemHandle(c->peer_inbox[r]);
+    if (c->inbox) cudaFree(c->inbox);
+    if (c->d_table) cudaFree(c->d_table);
     if (c->d_bases) cudaFree(c->d_bases);
     if (api && c->comm) api->CommDestroy(c->comm);
     delete c;
@@ -187,6 +241,14 @@ int lk_index_attach_comm(lk_index *idx, lk_comm *c, int64_t shard_base) {
     if (r != ncclSuccess) return fail(LK_ENCCL, std::string("ncclAllGather(bases): ") + api->GetErrorString(r));
     if (e != cudaSuccess) return fail(LK_ECUDA, std::string("lk_index_attach_comm: ") + cudaGetErrorString(e));
     c->bases_valid = true;
+    if (c->peer_ready) {
+        PeerTable t = {};
+        t.world = c->world;
+        t.rank = c->rank;
+        t.base = shard_base;
+        for (int r2 = 0; r2 < c->world; ++r2) t.inbox[r2] = c->peer_inbox[r2];
+        LK_CUDA(cudaMemcpy(c->d_table, &t, sizeof(t), cudaMemcpyHostToDevice));
+    }
     idx->comm = c;
     idx->shard_base = 0;  // ids stay local until the merge re-bases them
     return LK_OK;

@@ -15,4 +15,11 @@ struct ResultArena;
 // with the global result (ids are global row numbers).
 int comm_gather_merge(lk_comm *c, lk_index *idx, const ResultArena &res, int q_first, int nq, int k);
 
+// Device table for the in-kernel exchange over peer memory, or nullptr when it has not
+// been set up (or k is above its limit): the caller then uses comm_gather_merge.
+struct PeerTable;
+const PeerTable *comm_peer_table(lk_comm *c, int k);
+// Sequence number of the next sharded query (every rank issues the same queries in the same order).
+unsigned int comm_next_seq(lk_comm *c);
+
 }  // namespace lk

@@ -171,7 +171,7 @@ static int ensure_scan_scratch(lk_index *idx, int k) {
 // at most kMaxK; pass p accepts only keys below the last key of pass p-1.
 static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered, float cq, float qscale,
                          const int *d_slots, long long n_cand, int k_eff, int k_stride, int passes,
-                         const ResultArena &res, int qi) {
+                         const ResultArena &res, int qi, const PeerTable *peer = nullptr, unsigned int seq = 0) {
     for (int p = 0; p < passes; ++p) {
         const int done = p * kMaxK;
         const int kk = std::min(kMaxK, k_eff - done);
@@ -200,6 +200,8 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
         a.scales = idx->d_scales;
         a.qscale = qscale;
         a.shard_base = idx->shard_base;
+        a.peer = peer;
+        a.seq = seq;
         LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream));
         idx->scan_launches++;
     }
@@ -451,10 +453,13 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
         LK_CUDA(cudaMemcpyAsync(idx->d_slots.p, allow_slots, (size_t)n_cand * 4, cudaMemcpyHostToDevice, idx->stream));
         d_slots = (const int *)idx->d_slots.p;
     }
+    // sharded: exchange inside the scan kernel over peer memory when that is set up, else NCCL
+    const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
     for (int q = 0; q < nq; ++q)
         LK_TRY(enqueue_query(idx, (const unsigned char *)idx->d_query.p + (size_t)q * idx->qbytes, cen[q] != 0, cq[q],
-                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q));
-    if (sharded) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
+                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer,
+                             peer ? comm_next_seq(idx->comm) : 0u));
+    if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
     LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
     LK_TRY(unpack_results(idx->res, nq, k, k_eff, passes, out_ids, out_scores, out_iscores, out_counts));
@@ -611,11 +616,13 @@ int lk_search_resident(lk_index *idx, lk_queries *q, int first, int count, int k
     const int k_eff = sharded ? k : (int)std::min<long long>(k, idx->len);
     LK_TRY(ensure_scan_scratch(idx, k_eff));
     if (q->res.nq != q->nq || q->res.k != k_eff) LK_TRY(q->res.shape(q->nq, k_eff, 1));
+    const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
     for (int i = first; i < first + count; ++i) {
         LK_TRY(enqueue_query(idx, (const unsigned char *)q->d_query.p + (size_t)i * idx->qbytes, q->centered != 0,
-                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i));
-        // one query at a time: its candidates are exchanged and merged before the next scan starts
-        if (sharded) LK_TRY(comm_gather_merge(idx->comm, idx, q->res, i, 1, k_eff));
+                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i, peer,
+                             peer ? comm_next_seq(idx->comm) : 0u));
+        // one query at a time: without the peer path its candidates are gathered and merged here
+        if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, q->res, i, 1, k_eff));
     }
     return LK_OK;
 }

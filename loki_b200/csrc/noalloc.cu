@@ -102,5 +102,7 @@ extern "C" int lk_scan_i8_prealloc(int device, const int8_t *d_codes, int64_t n,
     a.scales = d_scales;
     a.qscale = query_scale;
     a.shard_base = 0;
+    a.peer = nullptr;
+    a.seq = 0;
     return scan_launch(SCAN_I8, a, plan, st);
 }

@@ -5,6 +5,23 @@
 
 namespace lk {
 
+// Direct exchange of per-shard results between the GPUs of one box (peer memory over
+// NVLink): every rank owns an inbox that all ranks can write.
+constexpr int kPeerSlots = 4;    // queries in flight before an inbox slot is reused
+constexpr int kPeerMaxWorld = 16;
+constexpr int kPeerMaxK = 128;   // larger k goes through the NCCL all-gather
+struct PeerInbox {
+    unsigned int flags[kPeerSlots][kPeerMaxWorld];                    // sequence number of the list present
+    unsigned int pad[64 - (kPeerSlots * kPeerMaxWorld) % 64];
+    unsigned long long keys[kPeerSlots][kPeerMaxWorld][kPeerMaxK];    // ranked keys, GLOBAL row ids
+    float payload[kPeerSlots][kPeerMaxWorld][kPeerMaxK];              // finished float score of int8 hits
+};
+struct PeerTable {                    // lives in device memory of each rank
+    int world, rank;
+    long long base;                   // first global row of this rank's shard
+    PeerInbox *inbox[kPeerMaxWorld];  // every rank's inbox as mapped into this process
+};
+
 // One scan = one query against n candidate rows, fused with top-k selection.
 struct ScanArgs {
     const unsigned char *rows;  // corpus base (device)
@@ -29,6 +46,8 @@ struct ScanArgs {
     const float *scales;        // int8: per-slot scale
     float qscale;               // int8: scale of the query
     long long shard_base;
+    const PeerTable *peer;      // nullptr, or: exchange the result with the other shards inside the kernel
+    unsigned int seq;           // sequence number of this query, the same on every rank
 };
 
 enum ScanType { SCAN_F32 = 0, SCAN_F16 = 1, SCAN_I8 = 2 };

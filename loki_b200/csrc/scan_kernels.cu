@@ -255,6 +255,8 @@ __device__ __forceinline__ void slab_accumulate_fixed(typename TR::acc_t (&acc)[
     }
 }
 
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // longest wait for another rank's list: 2 s
+
 // Shared tail of both scan kernels: publish this CTA's list; the last CTA to arrive
 // merges all lists and writes the result.
 template <int TYPE>
@@ -269,19 +271,105 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
     if (!*s_last) return;
     __threadfence();
     cand_select_from_lists(buf, a.part, (int)gridDim.x);
-    const int cnt = buf.ctrl->count;
-    for (int i = tid; i < a.k; i += T) {
-        const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
-        a.out_keys[i] = key;
-        float dq = 0.0f;
-        if (TYPE == SCAN_I8 && key != 0ull) dq = a.qscale * a.scales[key_slot(key)];
-        emit_hit(TYPE, key, i, a.shard_base, dq, a.out_ids, a.out_scores, a.out_iscores);
+    int cnt = buf.ctrl->count;
+    bool peer_timeout = false;
+    if (a.peer == nullptr) {
+        for (int i = tid; i < a.k; i += T) {
+            const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
+            a.out_keys[i] = key;
+            float dq = 0.0f;
+            if (TYPE == SCAN_I8 && key != 0ull) dq = a.qscale * a.scales[key_slot(key)];
+            emit_hit(TYPE, key, i, a.shard_base, dq, a.out_ids, a.out_scores, a.out_iscores);
+        }
+    } else {
+        // ---- sharded index: exchange with the other GPUs of the box, then merge ----
+        // This shard's ranked list goes straight into every rank's inbox over NVLink
+        // (plain stores to peer memory), followed by a release of the slot's flag; then
+        // this CTA waits (bounded) until all ranks' lists for this query have landed in
+        // its own inbox and merges them.  No collective launch, no host round trip.
+        const PeerTable &pt = *a.peer;
+        const int slot = (int)(a.seq % kPeerSlots);
+        const unsigned want = a.seq + 1u;
+        for (int i = tid; i < a.k; i += T) {
+            const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
+            a.out_keys[i] = key;
+            float pay = 0.0f;
+            if (TYPE == SCAN_I8 && key != 0ull)
+                pay = (float)i32_from_ord(key_ord(key)) * (a.qscale * a.scales[key_slot(key)]);
+            // the low word holds ~row: subtracting the shard base adds it to the row number
+            const unsigned long long gkey = key ? key - (unsigned long long)pt.base : 0ull;
+            for (int r = 0; r < pt.world; ++r) {
+                pt.inbox[r]->keys[slot][pt.rank][i] = gkey;
+                if (TYPE == SCAN_I8) pt.inbox[r]->payload[slot][pt.rank][i] = pay;
+            }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < pt.world) {
+            unsigned int *f = &pt.inbox[tid]->flags[slot][pt.rank];
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(want) : "memory");
+        }
+        __shared__ int s_peer_bad;
+        if (tid == 0) s_peer_bad = 0;
+        __syncthreads();
+        if (tid < pt.world) {
+            const unsigned int *f = &pt.inbox[pt.rank]->flags[slot][tid];
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (v == want) break;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > kPeerWaitNs) {  // a rank never delivered: give up, report, stay usable
+                    s_peer_bad = 1;
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+        __syncthreads();
+        peer_timeout = s_peer_bad != 0;
+        const PeerInbox *mine_in = pt.inbox[pt.rank];
+        cand_select_from_lists(buf, &mine_in->keys[slot][0][0], pt.world, kPeerMaxK);
+        cnt = buf.ctrl->count;
+        for (int i = tid; i < a.k; i += T) {
+            const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
+            if (key == 0ull) {
+                emit_hit(TYPE, 0ull, i, 0, 0.0f, a.out_ids, a.out_scores, a.out_iscores);
+                continue;
+            }
+            a.out_ids[i] = (long long)key_slot(key);  // already a global row number
+            if (TYPE != SCAN_I8) {
+                a.out_scores[i] = f32_from_ord(key_ord(key));
+                if (a.out_iscores) a.out_iscores[i] = 0;
+                continue;
+            }
+            // the float score was finished by the shard owning the row: find the key in the lists
+            float sc = 0.0f;
+            bool found = false;
+            for (int r = 0; r < pt.world && !found; ++r) {
+                int lo = 0, hi = a.k - 1;
+                while (lo <= hi) {  // ranked descending
+                    const int mid = (lo + hi) >> 1;
+                    const unsigned long long v = __ldcg(&mine_in->keys[slot][r][mid]);
+                    if (v == key) {
+                        sc = __ldcg(&mine_in->payload[slot][r][mid]);
+                        found = true;
+                        break;
+                    }
+                    if (v > key) lo = mid + 1; else hi = mid - 1;
+                }
+            }
+            a.out_scores[i] = sc;
+            if (a.out_iscores) a.out_iscores[i] = i32_from_ord(key_ord(key));
+        }
     }
     if (tid == 0) {
         // a CTA whose bounded wait ran out has raised the flag before publishing its list
-        const bool bad = a.error != nullptr && *(volatile int *)a.error != 0;
+        const bool bad = (a.error != nullptr && *(volatile int *)a.error != 0) || peer_timeout;
         *a.out_count = bad ? -1 : cnt;
-        if (bad) *a.error = 0;
+        if (a.error != nullptr) *a.error = 0;
         if (a.next_batch != nullptr) *a.next_batch = 0u;
         *a.ticket = 0u;
     }

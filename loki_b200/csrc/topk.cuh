@@ -104,8 +104,10 @@ __device__ __forceinline__ void cand_offer_warp(const CandBuf &b, bool pass, uns
 // offered again, so nothing is ever dropped.
 constexpr int kSelectUnroll = 16;
 
-__device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned long long *src, int lists) {
+__device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned long long *src, int lists,
+                                              int stride = 0) {
     const int tid = threadIdx.x, T = blockDim.x;
+    if (stride == 0) stride = b.k;  // list l starts at src[l * stride]; entries past k are ignored
     const long long total = (long long)lists * b.k;
     __shared__ int s_overflow;
     for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
@@ -118,7 +120,7 @@ __device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned l
     if (lists <= b.cap) {
         const int p = (b.k + lists - 1) / lists - 1;
         const int j = (b.k + p) / (p + 1);
-        for (int l = tid; l < lists; l += T) b.keys[l] = __ldcg(src + (size_t)l * b.k + p);
+        for (int l = tid; l < lists; l += T) b.keys[l] = __ldcg(src + (size_t)l * stride + p);
         __syncthreads();
         for (int l = tid; l < lists; l += T) {
             const unsigned long long h = b.keys[l];
@@ -135,7 +137,7 @@ __device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned l
 #pragma unroll
         for (int u = 0; u < kSelectUnroll; ++u) {
             const long long i = base + (long long)u * T + tid;
-            key[u] = (i < total) ? __ldcg(src + i) : 0ull;
+            key[u] = (i < total) ? __ldcg(src + (i / b.k) * stride + (i % b.k)) : 0ull;
         }
         for (;;) {
             const unsigned long long thr = *(volatile unsigned long long *)&b.ctrl->thr;

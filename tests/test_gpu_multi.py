@@ -32,18 +32,26 @@ uid = [lk.Comm.unique_id() if rank == 0 else None]
 dist.broadcast_object_list(uid, src=0)
 comm = lk.Comm(world, rank, rank, uid[0])
 out = {}
-for name, store in (("i8", lk.LK_I8), ("f32", lk.LK_F32)):
-    base, cnt = S.shard_bounds(n, world)[rank]
-    idx = lk.DeviceIndex(dim, store, device=rank)
-    idx.append(rows[base:base + cnt])
-    idx.attach_comm(comm, base)
-    ids, scores, iscores, counts = idx.search(queries, k)
-    rq = idx.queries(queries)
-    rq.enqueue(0, 5, k)
-    ids2, scores2, iscores2, counts2 = rq.fetch(0, 5, k)
-    assert np.array_equal(ids, ids2) and np.array_equal(scores, scores2) and np.array_equal(iscores, iscores2)
-    out[name + "_ids"], out[name + "_scores"], out[name + "_iscores"] = ids, scores, iscores
-    rq.close(); idx.close()
+for mode in ("nccl", "peer"):
+    if mode == "peer":  # switch the same communicator to the in-kernel exchange over peer memory
+        handles = [None] * world
+        dist.all_gather_object(handles, comm.peer_export())
+        comm.peer_attach(handles)
+    for name, store in (("i8", lk.LK_I8), ("f32", lk.LK_F32)):
+        base, cnt = S.shard_bounds(n, world)[rank]
+        idx = lk.DeviceIndex(dim, store, device=rank)
+        idx.append(rows[base:base + cnt])
+        idx.attach_comm(comm, base)
+        ids, scores, iscores, counts = idx.search(queries, k)
+        rq = idx.queries(queries)
+        rq.enqueue(0, 5, k)
+        ids2, scores2, iscores2, counts2 = rq.fetch(0, 5, k)
+        assert np.array_equal(ids, ids2) and np.array_equal(scores, scores2) and np.array_equal(iscores, iscores2)
+        out[f"{mode}_{name}_ids"], out[f"{mode}_{name}_scores"], out[f"{mode}_{name}_iscores"] = ids, scores, iscores
+        if mode == "peer":  # k above the peer path's limit falls back to the all-gather
+            big = idx.search(queries[:1], 300)
+            out[f"big_{name}_ids"] = big[0]
+        rq.close(); idx.close()
 np.savez(os.path.join(os.environ["LK_OUT"], f"rank{rank}.npz"), **out)
 dist.barrier()
 comm.close()
@@ -82,7 +90,10 @@ def test_sharded_search_over_nccl_equals_single_index(lk, tmp_path):
         idx = lk.DeviceIndex(dim, store)
         idx.append(rows)
         ids, scores, iscores, _ = idx.search(queries, k)
+        big = idx.search(queries[:1], 300)[0]
         for g in got:
-            assert np.array_equal(g[name + "_ids"], ids), name
-            assert np.array_equal(g[name + "_scores"], scores), name
-            assert np.array_equal(g[name + "_iscores"], iscores), name
+            for mode in ("nccl", "peer"):
+                assert np.array_equal(g[f"{mode}_{name}_ids"], ids), (mode, name)
+                assert np.array_equal(g[f"{mode}_{name}_scores"], scores), (mode, name)
+                assert np.array_equal(g[f"{mode}_{name}_iscores"], iscores), (mode, name)
+            assert np.array_equal(g[f"big_{name}_ids"], big), name
