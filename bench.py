@@ -41,6 +41,9 @@ if ROOT not in sys.path:
 ROWS_PER_GPU = 1_000_000
 DIM = 768
 TOPK = 10
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_scan_bulk launch on this workload,
+# from the ncu capture summarised in profiles/k_scan_bulk_int8_1Mx768_k10.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 771.8e6
 CHUNK = 62_500  # rows generated per torch call (192 MB of float32)
 
 
@@ -274,7 +277,8 @@ def run_ours(args):
                            "inside the scan kernel: each shard's top-10 stored into every rank's inbox over NVLink "
                            "(peer memory), merged by the last CTA")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "traffic_unit": "bytes per launch (ncu, 1 GPU)", "algorithmic_bytes": algo_bytes,
                          "note": "achieved = rows x 768 B / (timed region / K): launch gaps"
                                  + (", exchange and merge" if world > 1 else "") + " are inside the denominator"},
             "e2e": {"value": world * E / e2e_s, "unit": "queries/s", "steps": E,
