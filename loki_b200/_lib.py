@@ -131,7 +131,7 @@ class DeviceIndex:
         self._comm = None
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # lib is None during interpreter shutdown
             lib.lk_index_destroy(self._h)
             self._h = None
 
@@ -187,18 +187,19 @@ class DeviceIndex:
         if q.shape[1] != self.dim:
             raise LokiError(LK_EDIM, f"queries have {q.shape[1]} columns, index has dim {self.dim}")
         nq, kk = q.shape[0], max(int(k), 0)
-        ids = np.full((nq, kk), -1, np.int64)
-        scores = np.zeros((nq, kk), np.float32)
-        iscores = np.zeros((nq, kk), np.int32)
-        counts = np.zeros(nq, np.int32)
+        # the library writes every entry (misses are -1 / 0), so the outputs need no initialisation
+        ids = np.empty((nq, kk), np.int64)
+        scores = np.empty((nq, kk), np.float32)
+        iscores = np.empty((nq, kk), np.int32)
+        counts = np.empty(nq, np.int32)
         al, nal = None, 0
         if allow_slots is not None:
             al = np.ascontiguousarray(allow_slots, dtype=np.int32)
             nal = al.size
             if nal == 0:
                 al = np.zeros(1, np.int32)  # non-NULL pointer, zero entries: "allow nothing"
-        check(lib.lk_search(self._h, ptr(q), nq, int(k), int(scoring), ptr(al), nal,
-                            ptr(ids), ptr(scores), ptr(iscores), ptr(counts)))
+        check(lib.lk_search(self._h, q.ctypes.data, nq, int(k), int(scoring), ptr(al), nal,
+                            ids.ctypes.data, scores.ctypes.data, iscores.ctypes.data, counts.ctypes.data))
         return ids, scores, iscores, counts
 
     def search_shared(self, pos, posw=None, neg=None, negw=None, k: int = 10, scoring: int = LK_SCORE_DEFAULT,
@@ -263,7 +264,7 @@ class ResidentQueries:
         self._h, self.index, self.nq = h, index, q.shape[0]
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib.lk_queries_destroy(self._h)
             self._h = None
 

@@ -10,6 +10,7 @@
 //   part    grid x k ranking keys + one ticket word: scratch of the scan kernel
 //   result arena, query buffer, slot list, upload staging: grown on demand
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <mutex>
 #include <new>
@@ -136,6 +137,8 @@ static int maybe_recenter(lk_index *idx) {
 
 // Normalise one raw query and convert it to what the scan kernel reads.
 // Returns whether the query is scored centered.
+constexpr int kFastWaitMs = 2500;  // longer than any bounded wait inside a kernel
+
 static bool prepare_query(const lk_index *idx, const float *q, int scoring, unsigned char *dst,
                           float *cq, float *qscale) {
     const int d = idx->dim;
@@ -169,42 +172,115 @@ static int ensure_scan_scratch(lk_index *idx, int k) {
 
 // Enqueue the scan(s) of one prepared query.  k_eff hits are selected in passes of
 // at most kMaxK; pass p accepts only keys below the last key of pass p-1.
+// Arguments of one scan pass over this index (outputs and query are filled in by the caller).
+static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, const int *d_slots,
+                          long long n_cand, int k) {
+    ScanArgs a;
+    a.rows = idx->d_rows;
+    a.ld = idx->ld;
+    a.chunks = idx->chunks;
+    a.n = n_cand;
+    a.slots = d_slots;
+    a.query = nullptr;
+    a.cnorm = centered ? idx->d_cnorm : nullptr;
+    a.cq = cq;
+    a.k = k;
+    a.bound = nullptr;
+    a.part = (unsigned long long *)idx->part.p;
+    a.ticket = idx->d_ticket;
+    a.error = (int *)(idx->d_ticket + 1);
+    // consecutive launches may overlap at their edges: each uses its own batch counter
+    a.next_batch = idx->d_ticket + 2 + (idx->scan_launches & 3);
+    a.scales = idx->d_scales;
+    a.qscale = qscale;
+    a.shard_base = idx->shard_base;
+    a.peer = nullptr;
+    a.seq = 0;
+    a.done_flag = nullptr;
+    a.done_value = 0;
+    return a;
+}
+
+// Enqueue the scan(s) of one prepared query.  k_eff hits are selected in passes of
+// at most kMaxK; pass p accepts only keys below the last key of pass p-1.
 static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered, float cq, float qscale,
                          const int *d_slots, long long n_cand, int k_eff, int k_stride, int passes,
                          const ResultArena &res, int qi, const PeerTable *peer = nullptr, unsigned int seq = 0) {
     for (int p = 0; p < passes; ++p) {
         const int done = p * kMaxK;
-        const int kk = std::min(kMaxK, k_eff - done);
-        ScanArgs a;
-        a.rows = idx->d_rows;
-        a.ld = idx->ld;
-        a.chunks = idx->chunks;
-        a.n = n_cand;
-        a.slots = d_slots;
+        ScanArgs a = base_args(idx, centered, cq, qscale, d_slots, n_cand, std::min(kMaxK, k_eff - done));
         a.query = d_q;
-        a.cnorm = centered ? idx->d_cnorm : nullptr;
-        a.cq = cq;
-        a.k = kk;
         const size_t o = (size_t)qi * k_stride + done;
         a.bound = (p == 0) ? nullptr : res.d_keys() + o - 1;
-        a.part = (unsigned long long *)idx->part.p;
-        a.ticket = idx->d_ticket;
-        a.error = (int *)(idx->d_ticket + 1);
-        // consecutive launches may overlap at their edges: each uses its own batch counter
-        a.next_batch = idx->d_ticket + 2 + (idx->scan_launches & 3);
         a.out_keys = res.d_keys() + o;
         a.out_ids = res.d_ids() + o;
         a.out_scores = res.d_scores() + o;
         a.out_iscores = res.d_iscores() + o;
         a.out_count = res.d_counts() + (size_t)qi * passes + p;
-        a.scales = idx->d_scales;
-        a.qscale = qscale;
-        a.shard_base = idx->shard_base;
         a.peer = peer;
         a.seq = seq;
         LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream));
         idx->scan_launches++;
     }
+    return 0;
+}
+
+// Lowest-latency form of a single query: the prepared query rides in the launch
+// parameters (no upload), the kernel writes the k results straight into mapped pinned
+// host memory and releases a flag the host is polling (no download, no stream sync).
+constexpr int kFastMaxK = 1024;
+static int search_one_fast(lk_index *idx, const float *query, int scoring, const int *d_slots, long long n_cand,
+                           int k_eff, const PeerTable *peer, int k_user, int64_t *out_ids, float *out_scores,
+                           int32_t *out_iscores, int32_t *out_counts) {
+    const size_t off_scores = (size_t)kFastMaxK * 8, off_iscores = off_scores + (size_t)kFastMaxK * 4;
+    const size_t off_count = off_iscores + (size_t)kFastMaxK * 4, off_flag = off_count + 4;
+    const void *zc_before = idx->zc.p;
+    LK_TRY(idx->zc.reserve(off_flag + 4));
+    if (idx->zc.p != zc_before) memset(idx->zc.p, 0, off_flag + 4);  // the flag must not start at a live value
+    LK_TRY(idx->res.shape(1, k_eff, 1));  // device home of the ranked keys
+    char *z = (char *)idx->zc.p;
+    volatile unsigned int *flag = (volatile unsigned int *)(z + off_flag);
+    float cq = 0.0f, qscale = 0.0f;
+    ScanArgs a = base_args(idx, false, 0.0f, 0.0f, d_slots, n_cand, k_eff);
+    const bool centered = prepare_query(idx, query, scoring, a.query_inline, &cq, &qscale);
+    a.cnorm = centered ? idx->d_cnorm : nullptr;
+    a.cq = cq;
+    a.qscale = qscale;
+    a.out_keys = idx->res.d_keys();
+    a.out_ids = (long long *)z;
+    a.out_scores = (float *)(z + off_scores);
+    a.out_iscores = (int *)(z + off_iscores);
+    a.out_count = (int *)(z + off_count);
+    a.peer = peer;
+    a.seq = peer ? comm_next_seq(idx->comm) : 0u;
+    a.done_flag = (unsigned int *)(z + off_flag);
+    a.done_value = ++idx->zc_seq ? idx->zc_seq : ++idx->zc_seq;  // never 0
+    LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream));
+    idx->scan_launches++;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (unsigned spins = 0; *flag != a.done_value; ++spins) {
+        __builtin_ia32_pause();
+        if ((spins & 0xfff) == 0xfff &&
+            std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(kFastWaitMs)) {
+            // not there yet: let the runtime tell whether the launch failed
+            LK_CUDA(cudaStreamSynchronize(idx->stream));
+            if (*flag != a.done_value) return fail(LK_ETIMEOUT, "lk_search: the scan finished without delivering its results");
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    int cnt = *(volatile int *)(z + off_count);
+    if (cnt < 0) return fail(LK_ETIMEOUT, "a scan kernel gave up on a bounded wait (bulk copy or another rank); results are not valid");
+    if (cnt > k_eff) cnt = k_eff;
+    const long long *ids = (const long long *)z;
+    const float *sc = (const float *)(z + off_scores);
+    const int *isc = (const int *)(z + off_iscores);
+    for (int i = 0; i < k_user; ++i) {
+        const bool hit = i < cnt;
+        if (out_ids) out_ids[i] = hit ? (int64_t)ids[i] : -1;
+        if (out_scores) out_scores[i] = hit ? sc[i] : 0.0f;
+        if (out_iscores) out_iscores[i] = hit ? isc[i] : 0;
+    }
+    if (out_counts) out_counts[0] = cnt;
     return 0;
 }
 
@@ -310,6 +386,7 @@ int lk_index_destroy(lk_index *idx) {
     idx->d_slots.release();
     idx->d_stage.release();
     idx->h_query.release();
+    idx->zc.release();
     idx->gather.release();
     if (idx->ev0) cudaEventDestroy(idx->ev0);
     if (idx->ev1) cudaEventDestroy(idx->ev1);
@@ -436,6 +513,19 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     const int passes = (k_eff + kMaxK - 1) / kMaxK;
     if (sharded && passes > 1) return fail(LK_ERANGE, "lk_search: k above the single-pass limit is not supported on a sharded index");
     LK_TRY(ensure_scan_scratch(idx, std::min(k_eff, kMaxK)));
+    const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
+    if (nq == 1 && passes == 1 && k_eff <= kFastMaxK && idx->qbytes <= kInlineQueryBytes && (!sharded || peer)) {
+        const int *d_sl = nullptr;
+        if (filtered && n_cand > 0) {
+            LK_TRY(idx->d_slots.reserve((size_t)n_cand * 4));
+            LK_CUDA(cudaMemcpyAsync(idx->d_slots.p, allow_slots, (size_t)n_cand * 4, cudaMemcpyHostToDevice, idx->stream));
+            d_sl = (const int *)idx->d_slots.p;
+        }
+        LK_TRY(search_one_fast(idx, queries, scoring, d_sl, n_cand, k_eff, peer, k, out_ids, out_scores, out_iscores,
+                               out_counts));
+        idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        return LK_OK;
+    }
     LK_TRY(idx->res.shape(nq, k_eff, passes));
 
     // queries: prepare on the host, one upload
@@ -454,7 +544,6 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
         d_slots = (const int *)idx->d_slots.p;
     }
     // sharded: exchange inside the scan kernel over peer memory when that is set up, else NCCL
-    const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
     for (int q = 0; q < nq; ++q)
         LK_TRY(enqueue_query(idx, (const unsigned char *)idx->d_query.p + (size_t)q * idx->qbytes, cen[q] != 0, cq[q],
                              qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer,

@@ -129,6 +129,8 @@ struct lk_index {
     lk::ResultArena res;
     lk::DevBuf d_query, d_slots, d_stage;
     lk::PinnedBuf h_query;
+    lk::PinnedBuf zc;           // mapped pinned block the kernel writes single-query results into
+    unsigned int zc_seq = 0;
     // multi-GPU
     lk_comm *comm = nullptr;
     long long shard_base = 0;

@@ -104,5 +104,7 @@ extern "C" int lk_scan_i8_prealloc(int device, const int8_t *d_codes, int64_t n,
     a.shard_base = 0;
     a.peer = nullptr;
     a.seq = 0;
+    a.done_flag = nullptr;
+    a.done_value = 0;
     return scan_launch(SCAN_I8, a, plan, st);
 }

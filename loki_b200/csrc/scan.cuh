@@ -22,6 +22,8 @@ struct PeerTable {                    // lives in device memory of each rank
     PeerInbox *inbox[kPeerMaxWorld];  // every rank's inbox as mapped into this process
 };
 
+constexpr int kInlineQueryBytes = 3072;  // int8 rows up to 3072 B, float32 up to 768 elements
+
 // One scan = one query against n candidate rows, fused with top-k selection.
 struct ScanArgs {
     const unsigned char *rows;  // corpus base (device)
@@ -48,6 +50,12 @@ struct ScanArgs {
     long long shard_base;
     const PeerTable *peer;      // nullptr, or: exchange the result with the other shards inside the kernel
     unsigned int seq;           // sequence number of this query, the same on every rank
+    // Low-latency single query: outputs may point into mapped pinned host memory; after they
+    // are written the kernel releases *done_flag = done_value for a host that is polling it.
+    unsigned int *done_flag;    // nullptr = none
+    unsigned int done_value;
+    // query == nullptr: the prepared query travels in the launch parameters instead
+    alignas(16) unsigned char query_inline[kInlineQueryBytes];
 };
 
 enum ScanType { SCAN_F32 = 0, SCAN_F16 = 1, SCAN_I8 = 2 };

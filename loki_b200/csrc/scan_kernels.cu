@@ -365,6 +365,10 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
             if (a.out_iscores) a.out_iscores[i] = i32_from_ord(key_ord(key));
         }
     }
+    if (a.done_flag != nullptr) {  // results may sit in host memory: make them visible there first
+        __threadfence_system();
+        __syncthreads();
+    }
     if (tid == 0) {
         // a CTA whose bounded wait ran out has raised the flag before publishing its list
         const bool bad = (a.error != nullptr && *(volatile int *)a.error != 0) || peer_timeout;
@@ -372,6 +376,10 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
         if (a.error != nullptr) *a.error = 0;
         if (a.next_batch != nullptr) *a.next_batch = 0u;
         *a.ticket = 0u;
+        if (a.done_flag != nullptr) {
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.done_flag), "r"(a.done_value) : "memory");
+        }
     }
 }
 
@@ -394,7 +402,7 @@ __device__ __forceinline__ bool cand_rendezvous(const CandBuf &buf, bool work, b
 // global memory.  Used for allow-list (gathered) scans and for small inputs.
 // ---------------------------------------------------------------------------
 template <class TR, int TYPE, int G>
-__global__ void __launch_bounds__(kScanThreads, 2) k_scan(const ScanArgs a) {
+__global__ void __launch_bounds__(kScanThreads, 2) k_scan(const __grid_constant__ ScanArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int R = (G < TR::kRows) ? G : TR::kRows;
 
@@ -414,7 +422,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const ScanArgs a) {
         buf.ctrl->n_done = 0;
         buf.ctrl->thr = 0ull;
     }
-    TR::stage_query(qs, a.query, a.chunks);
+    TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
     const unsigned long long bound = a.bound ? __ldcg(a.bound) : ~0ull;
     __syncthreads();
 
@@ -523,7 +531,7 @@ __device__ __forceinline__ void tl_stamp(int i) {
 #endif
 
 template <class TR, int TYPE, int G, int WARPS, int SC, bool QREG>
-__global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, int slab_bytes_rt, int n_slabs_rt) {
+__global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_constant__ ScanArgs a, int slab_bytes_rt, int n_slabs_rt) {
     const int slab_bytes = SC > 0 ? SC * 16 : slab_bytes_rt;
     const int n_slabs = QREG ? 1 : n_slabs_rt;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -624,7 +632,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const ScanArgs a, i
         buf.ctrl->n_done = 0;
         buf.ctrl->thr = 0ull;
     }
-    TR::stage_query(qs, a.query, a.chunks);
+    TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
     unsigned long long bound = ~0ull;
     if (a.bound != nullptr) {  // a later pass of a large-k search: its bound is the previous pass's output
         asm volatile("griddepcontrol.wait;" ::: "memory");
