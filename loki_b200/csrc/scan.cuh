@@ -79,6 +79,13 @@ struct ScanPlan {
     int n_slabs = 1;       // stages per 32-row batch
     int fixed_chunks = 0;  // > 0: slab width (in 16-byte chunks) has a compile-time kernel
     size_t bulk_smem = 0;
+    // TMA-staged kernel for wide rows (ld a multiple of 512 B, >= 1 KB): whole-row batches
+    bool wide_ok = false;
+    int wide_nj = 0;       // 512-byte units per row
+    int wide_rows = 0;     // rows per batch
+    int wide_warps = 0;
+    int wide_run = 1;      // consecutive batches handed out per counter access
+    size_t wide_smem = 0;
 };
 int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan);
 int scan_max_grid(const ScanPlan &plan);   // CTAs to size the per-CTA list scratch for

@@ -93,11 +93,29 @@ struct TraitsF32 {
     }
     // float32 x float32 products are exact in float64, so fma here equals the
     // reference's multiply-then-add; only the order of the additions differs.
+#ifdef LK_F32_INTCVT
+    // float32 -> float64 widening with integer ops (exact for normal numbers and zero;
+    // denormals flush to zero, inf/nan are not handled): tuning experiment only
+    __device__ __forceinline__ static double widen(int b) {
+        const unsigned u = (unsigned)b;
+        unsigned hi = ((u >> 3) & 0x0fffffffu) + 0x38000000u;
+        hi = ((u & 0x7f800000u) == 0u) ? 0u : hi;
+        hi |= u & 0x80000000u;
+        const unsigned lo = ((u & 0x7f800000u) == 0u) ? 0u : (u << 29);
+        return __hiloint2double((int)hi, (int)lo);
+    }
+#else
+    __device__ __forceinline__ static double widen(int b) { return (double)__int_as_float(b); }
+#endif
     __device__ __forceinline__ static void dot(acc_t &acc, const int4 &v, const QChunk &c) {
-        acc = fma((double)__int_as_float(v.x), c.a.x, acc);
-        acc = fma((double)__int_as_float(v.y), c.a.y, acc);
-        acc = fma((double)__int_as_float(v.z), c.b.x, acc);
-        acc = fma((double)__int_as_float(v.w), c.b.y, acc);
+#ifdef LK_EXP_NODOT
+        acc += __hiloint2double(v.x ^ v.y, v.z ^ v.w) + c.a.x;
+#else
+        acc = fma(widen(v.x), c.a.x, acc);
+        acc = fma(widen(v.y), c.a.y, acc);
+        acc = fma(widen(v.z), c.b.x, acc);
+        acc = fma(widen(v.w), c.b.y, acc);
+#endif
     }
     __device__ __forceinline__ static acc_t shfl(acc_t v, int m) {
         return __longlong_as_double((long long)shfl_xor_u64((uint64_t)__double_as_longlong(v), m));
@@ -741,6 +759,191 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
+// TMA-staged scan for WIDE rows (ld a multiple of 512 bytes, 1 KB and up).
+// A batch is RB whole rows = one contiguous bulk copy of RB * ld bytes.  All 32
+// lanes share a row: lane l reads 16-byte chunks l, l+32, ... (NJ of them), keeps
+// one accumulator per row of the batch and the query chunks it needs in registers.
+// Float rows pay one float32->float64 conversion per element on a 16-lane-per-clock
+// pipe, whose latency a single warp per scheduler cannot hide: the float kernels
+// run 8 warps per CTA with half-size stages, the int8 kernel 4.
+// Batches are handed out in runs of `run` consecutive batches per counter access.
+// ---------------------------------------------------------------------------
+template <class TR, int RB>
+__device__ __forceinline__ typename TR::acc_t wide_reduce(typename TR::acc_t (&acc)[RB], int lane) {
+    using acc_t = typename TR::acc_t;
+    // plain halving down to RB lanes per value, then the transposed butterfly
+#pragma unroll
+    for (int w = 16; w >= RB; w >>= 1) {
+#pragma unroll
+        for (int i = 0; i < RB; ++i) acc[i] = acc[i] + TR::shfl(acc[i], w);
+    }
+#pragma unroll
+    for (int w = RB / 2; w >= 1; w >>= 1) {
+        const bool upper = (lane & w) != 0;
+#pragma unroll
+        for (int i = 0; i < w; ++i) {
+            const acc_t send = upper ? acc[i] : acc[i + w];
+            const acc_t keep = upper ? acc[i + w] : acc[i];
+            acc[i] = keep + TR::shfl(send, w);
+        }
+    }
+    return acc[0];  // lane i (mod RB) holds row i
+}
+
+template <class TR, int TYPE, int WARPS, int RB, int NJ>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_constant__ ScanArgs a, int run) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int T = WARPS * 32;
+    constexpr int LD = NJ * 512;
+    constexpr int STAGE = RB * LD;
+    using acc_t = typename TR::acc_t;
+
+    CandBuf buf;
+    buf.k = a.k;
+    buf.cap = cand_capacity(a.k);
+    buf.limit = buf.cap - kScanThreads;
+    buf.keys = reinterpret_cast<unsigned long long *>(smem);
+    buf.ctrl = reinterpret_cast<CandCtrl *>(smem + (size_t)buf.cap * 8);
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem + (size_t)buf.cap * 8 + 16);
+    unsigned char *qs = smem + (size_t)buf.cap * 8 + 16 + WARPS * kBulkStages * 8;
+    const size_t q_bytes = (size_t)a.chunks * TR::kQBytes;
+    unsigned char *stages = smem + (((size_t)buf.cap * 8 + 16 + WARPS * kBulkStages * 8 + q_bytes + 127) & ~(size_t)127);
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        for (int i = 0; i < WARPS * kBulkStages; ++i) mbar_init(&bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const long long n_batches = (a.n + RB - 1) / RB;
+    unsigned char *my_stages = stages + (size_t)warp * kBulkStages * STAGE;
+    unsigned long long *my_bars = bars + warp * kBulkStages;
+
+    // batch hand-out: the first run of every warp is fixed, later runs come from the counter
+    const long long static_run = (long long)blockIdx.x * WARPS + warp;
+    const long long first_dynamic = (long long)gridDim.x * WARPS;
+    long long run_next = 0, run_end = 0;  // batches [run_next, run_end) of the current run
+    bool first = true, exhausted = false;
+    long long stage_batch[kBulkStages];
+#pragma unroll
+    for (int s = 0; s < kBulkStages; ++s) stage_batch[s] = -1;
+    auto issue = [&](int s) {  // whole warp
+        if (run_next >= run_end && !exhausted) {
+            long long r;
+            if (first) {
+                r = static_run;
+                first = false;
+            } else {
+                unsigned d = 0;
+                if (lane == 0) d = atomicAdd(a.next_batch, 1u);
+                r = first_dynamic + (long long)__shfl_sync(0xffffffffu, d, 0);
+            }
+            run_next = r * run;
+            run_end = min(run_next + run, n_batches);
+            if (run_next >= n_batches) exhausted = true;
+        }
+        const long long b = (!exhausted && run_next < run_end) ? run_next++ : -1;
+#pragma unroll
+        for (int i = 0; i < kBulkStages; ++i)
+            if (i == s) stage_batch[i] = b;
+        if (b < 0) return;
+        if (lane == 0) {
+            const long long row0 = b * RB;
+            const unsigned bytes = (unsigned)(min((long long)RB, a.n - row0) * LD);
+            mbar_expect_tx(&my_bars[s], bytes);
+            bulk_load(my_stages + (size_t)s * STAGE, a.rows + (size_t)row0 * LD, bytes, &my_bars[s]);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < kBulkStages; ++s) issue(s);
+
+    for (int i = tid; i < buf.cap; i += T) buf.keys[i] = 0ull;
+    if (tid == 0) {
+        buf.ctrl->count = 0;
+        buf.ctrl->n_done = 0;
+        buf.ctrl->thr = 0ull;
+    }
+    TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
+    unsigned long long bound = ~0ull;
+    if (a.bound != nullptr) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        bound = __ldcg(a.bound);
+    }
+    __syncthreads();
+    typename TR::QChunk q[NJ];
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) q[jj] = TR::load_q(qs, lane + jj * 32, a.chunks);
+
+    long long m = 0;
+    bool counted = false, failed = false;
+    for (;;) {
+        const int s = (int)(m % kBulkStages);
+        long long b = -1;
+#pragma unroll
+        for (int i = 0; i < kBulkStages; ++i)
+            if (i == s) b = stage_batch[i];
+        const bool work = b >= 0 && !failed;
+        int seen = 0;
+        if (lane == 0) seen = *(volatile int *)&buf.ctrl->count;
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (work && seen <= buf.limit) {
+            const unsigned parity = (unsigned)((m / kBulkStages) & 1);
+            unsigned spins = 0;
+            bool ready = false;
+            while (!(ready = mbar_try_wait(&my_bars[s], parity)) && ++spins < kBulkSpinLimit) {}
+            if (!__all_sync(0xffffffffu, ready)) {
+                if (lane == 0 && a.error != nullptr) atomicExch(a.error, 1);
+                failed = true;
+                continue;
+            }
+            const unsigned char *base = my_stages + (size_t)s * STAGE + (size_t)lane * 16;
+            acc_t acc[RB];
+#pragma unroll
+            for (int r = 0; r < RB; ++r) acc[r] = (acc_t)0;
+            // rows past the end of a short last batch hold stale bytes and are dropped by `valid`
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+#pragma unroll
+                for (int jj = 0; jj < NJ; ++jj) {
+                    const int4 v = *reinterpret_cast<const int4 *>(base + r * LD + jj * 512);
+                    TR::dot(acc[r], v, q[jj]);
+                }
+            }
+            __syncwarp();  // all lanes have the stage in registers: refill it
+            issue(s);
+            ++m;
+            const acc_t total = wide_reduce<TR, RB>(acc, lane);
+            const long long row = b * RB + (lane % RB);
+            const bool valid = lane < RB && row < a.n;
+            const unsigned slot = (unsigned)row;
+            unsigned long long key = 0ull;
+            if (valid) key = make_key(TR::finish(total, a, slot), slot);
+            const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
+            cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            continue;
+        }
+        if (cand_rendezvous(buf, work, counted, lane, WARPS)) break;
+    }
+    if (failed) {
+        for (long long mm = m; mm < m + kBulkStages; ++mm) {
+            long long b = -1;
+#pragma unroll
+            for (int i = 0; i < kBulkStages; ++i)
+                if (i == (int)(mm % kBulkStages)) b = stage_batch[i];
+            if (b < 0) continue;
+            unsigned spins = 0;
+            while (!mbar_try_wait(&my_bars[mm % kBulkStages], (unsigned)((mm / kBulkStages) & 1)) &&
+                   ++spins < kBulkSpinLimit) {}
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    publish_and_finish<TYPE>(a, buf, &s_last);
+}
+
+// ---------------------------------------------------------------------------
 // Merge of ranked lists (after the all-gather of per-shard candidates)
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kScanThreads, 1) k_merge_lists(const MergeArgs a) {
@@ -885,6 +1088,34 @@ static bulk_fn pick_bulk(int type, const ScanPlan &p) {
     }
 }
 
+typedef void (*wide_fn)(const ScanArgs, int);
+
+constexpr int kWideWarpsInt = 4, kWideWarpsFloat = 8;
+
+// (rows per batch, 512-byte units per row) -> kernel, for the widths that have one
+template <class TR, int TYPE, int WARPS, int RB>
+static wide_fn pick_wide_nj(int nj) {
+    switch (nj) {
+        case 2: return k_scan_wide<TR, TYPE, WARPS, (RB * 2 > 32 ? 32 : RB * 2), 2>;
+        case 3: return k_scan_wide<TR, TYPE, WARPS, (RB * 2 > 32 ? 32 : RB * 2), 3>;
+        case 4: return k_scan_wide<TR, TYPE, WARPS, RB, 4>;
+        case 6: return k_scan_wide<TR, TYPE, WARPS, RB, 6>;
+        case 8: return k_scan_wide<TR, TYPE, WARPS, RB / 2, 8>;
+        default: return nullptr;
+    }
+}
+static int wide_rows(int type, int nj) {  // must mirror pick_wide_nj
+    const int rb = (type == SCAN_I8) ? 8 : 4;
+    return nj <= 3 ? rb * 2 : (nj == 8 ? rb / 2 : rb);
+}
+static wide_fn pick_wide(int type, int nj) {
+    switch (type) {
+        case SCAN_I8: return pick_wide_nj<TraitsI8, SCAN_I8, kWideWarpsInt, 8>(nj);
+        case SCAN_F32: return pick_wide_nj<TraitsF32, SCAN_F32, kWideWarpsFloat, 4>(nj);
+        default: return pick_wide_nj<TraitsF16, SCAN_F16, kWideWarpsFloat, 4>(nj);
+    }
+}
+
 int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
     ScanPlan p;
     int sms = 0;
@@ -918,6 +1149,22 @@ int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
                   (size_t)kBulkWarps * kBulkStages * 32 * p.slab_bytes;
     p.bulk_ok = p.bulk_smem <= kSmemLimit;
     p.bulk_grid = sms;
+    // wide rows: whole-row batches (k_scan_wide)
+    p.wide_nj = (ld >= 1024 && ld % 512 == 0) ? ld / 512 : 0;
+    if (p.wide_nj > 0 && pick_wide(type, p.wide_nj) != nullptr) {
+        p.wide_warps = (type == SCAN_I8) ? kWideWarpsInt : kWideWarpsFloat;
+        p.wide_rows = wide_rows(type, p.wide_nj);
+        const size_t stage = (size_t)p.wide_rows * ld;
+        p.wide_smem = ((head + p.wide_warps * kBulkStages * 8 + q + 127) & ~(size_t)127) +
+                      (size_t)p.wide_warps * kBulkStages * stage;
+        p.wide_run = (int)std::max<size_t>(1, (size_t)24576 / stage);
+        if (p.wide_smem <= kSmemLimit) {
+            e = cudaFuncSetAttribute((const void *)pick_wide(type, p.wide_nj),
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.wide_smem);
+            if (e != cudaSuccess) return fail(4, std::string("scan plan (wide): ") + cudaGetErrorString(e));
+            p.wide_ok = true;
+        }
+    }
     if (p.bulk_ok) {
         bulk_fn fn = pick_bulk(type, p);
         e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.bulk_smem);
@@ -931,7 +1178,23 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
     const long long batches = (a.n + 31) / 32;
     // the TMA-staged kernel needs whole, contiguous rows and enough batches to fill its pipeline
     const bool bulk = plan.bulk_ok && a.slots == nullptr && batches >= (long long)plan.bulk_grid * kBulkWarps;
-    if (bulk) {
+    const bool wide = plan.wide_ok && a.slots == nullptr &&
+                      a.n >= (long long)plan.bulk_grid * plan.wide_warps * plan.wide_rows * plan.wide_run * 2;
+    if (wide) {
+        wide_fn fn = pick_wide(type, plan.wide_nj);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)plan.bulk_grid);
+        cfg.blockDim = dim3(plan.wide_warps * 32);
+        cfg.dynamicSmemBytes = plan.wide_smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t le = cudaLaunchKernelEx(&cfg, fn, a, plan.wide_run);
+        if (le != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(le));
+    } else if (bulk) {
         bulk_fn fn = pick_bulk(type, plan);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)plan.bulk_grid);
