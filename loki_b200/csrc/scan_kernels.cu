@@ -421,7 +421,7 @@ __device__ __forceinline__ bool cand_rendezvous(const CandBuf &buf, bool work, b
 // ---------------------------------------------------------------------------
 template <class TR, int TYPE, int G>
 __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const __grid_constant__ ScanArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
     constexpr int R = (G < TR::kRows) ? G : TR::kRows;
 
     CandBuf buf;
@@ -947,7 +947,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
 // Merge of ranked lists (after the all-gather of per-shard candidates)
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kScanThreads, 1) k_merge_lists(const MergeArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
     CandBuf buf;
     buf.k = a.k;
     buf.cap = cand_capacity(a.k);

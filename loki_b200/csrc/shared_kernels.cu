@@ -20,7 +20,7 @@ namespace lk {
 
 template <int TP>  // TP = power of two >= number of terms
 __global__ void __launch_bounds__(kScanThreads, 1) k_scan_shared(const SharedArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
     constexpr int R = (32 / TP) < 4 ? (32 / TP < 1 ? 1 : 32 / TP) : 4;
     constexpr int NV = R * TP;  // accumulators per lane
     CandBuf buf;

@@ -132,6 +132,46 @@ __device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned l
         for (int l = tid; l < lists; l += T) b.keys[l] = 0ull;
         __syncthreads();
     }
+    // Fast path: the lists are ranked, so the keys above the starting threshold are a
+    // prefix of each list.  One thread per list finds its prefix length by bisection
+    // (log2 k dependent loads instead of k); if all prefixes fit in the buffer together
+    // they are copied in and one sort finishes the job.
+    __shared__ int s_total;
+    const unsigned long long thr0 = b.ctrl->thr;
+    if (thr0 != 0ull) {
+        if (tid == 0) s_total = 0;
+        __syncthreads();
+        for (int l0 = 0; l0 < lists; l0 += T) {
+            const int l = l0 + tid;
+            int cut = 0;
+            if (l < lists) {
+                const unsigned long long *lst = src + (size_t)l * stride;
+                int lo = 0, hi = b.k;  // first index whose key is <= thr0 lies in [lo, hi]
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (__ldcg(lst + mid) > thr0) lo = mid + 1; else hi = mid;
+                }
+                cut = lo;
+            }
+            const int at = (cut > 0) ? atomicAdd(&s_total, cut) : 0;
+            if (cut > 0 && at + cut <= b.cap) {
+                const unsigned long long *lst = src + (size_t)l * stride;
+                for (int i = 0; i < cut; ++i) b.keys[at + i] = __ldcg(lst + i);
+            }
+        }
+        __syncthreads();
+        const int tot = s_total;
+        __syncthreads();
+        if (tot <= b.cap) {
+            if (tid == 0) b.ctrl->count = tot;
+            __syncthreads();
+            cand_prune(b);
+            return;
+        }
+        // too many survivors for one buffer: start over with the streaming pass below
+        for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
+        __syncthreads();
+    }
     for (long long base = 0; base < total; base += (long long)T * kSelectUnroll) {
         unsigned long long key[kSelectUnroll];
 #pragma unroll
