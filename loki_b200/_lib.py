@@ -92,6 +92,7 @@ _sig("lk_index_set_shard_base", _int, _vp, _i64)
 _sig("lk_hamming_pairs", _int, _vp, _i64, _int, _int, _int, _int, _vp, _i64, C.POINTER(_i64))
 _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64, C.POINTER(_i64))
 _sig("lk_stats", _int, _vp, C.POINTER(lk_stats_t))
+_sig("lk_index_set_batch_mode", _int, _vp, _int)
 _sig("lk_scan_i8_prealloc", _int, _int, _vp, _i64, _int, _i64, _vp, _vp, C.c_float, _int, _vp, _vp, _vp, _vp, _vp)
 LK_PREALLOC_MAX_K = 128
 
@@ -242,6 +243,11 @@ class DeviceIndex:
     def attach_comm(self, comm: "Comm", shard_base: int):
         check(lib.lk_index_attach_comm(self._h, comm._h if comm is not None else None, int(shard_base)))
         self._comm = comm
+
+    def set_batch_mode(self, tensor_cores: bool):
+        """Batches of >= 32 queries on an int8 index: tensor-core matrix product (True, default)
+        or consecutive single-query scans (False); results are identical."""
+        check(lib.lk_index_set_batch_mode(self._h, 1 if tensor_cores else 0))
 
     def set_shard_base(self, base: int):
         check(lib.lk_index_set_shard_base(self._h, int(base)))

@@ -104,6 +104,8 @@ int comm_gather_merge(lk_comm *c, lk_index *idx, const ResultArena &res, int q_f
     MergeArgs m;
     m.keys = (const unsigned long long *)g;
     m.payload = i8 ? (const float *)(g + pay_off) : nullptr;
+    m.qscales = nullptr;
+    m.scales = nullptr;
     m.scratch = (unsigned long long *)(g + scr_off);
     m.list_base = c->d_bases;
     m.lists = c->world;

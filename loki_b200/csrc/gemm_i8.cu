@@ -1,0 +1,460 @@
+// Batched int8 search: many queries against the corpus as an int8 x int8 -> int32
+// matrix product on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators
+// in tensor memory), with the top-k selection fused into the epilogue so that the
+// rows x queries score matrix never exists in memory.
+//
+// The reference scores one query at a time (media-server/embedindex/embedindex.go:424-457);
+// a batch of queries turns the same arithmetic into a dense contraction, which is the
+// one place on this path where tensor cores are the right tool.  Scores are the exact
+// int32 dots of the single-query scan, and ranking uses the same 64-bit keys, so the
+// result is bit-identical to running the queries one by one.
+//
+// Shape of one CTA (192 threads, one CTA per SM):
+//   warp 0     TMA producer: 2-D tiled loads (128-byte swizzle) of corpus tiles
+//              [128 rows x 128 K-bytes] into a ring of stages; loads the CTA's query
+//              tile [128 queries x all K] once, it stays resident in shared memory
+//   warp 1     allocates tensor memory and issues the MMAs: D[128 rows x 128 queries]
+//              += A[128 x 32] * B[128 x 32]^T, four per 128-byte K slice; commits free
+//              the stage / publish the accumulator through mbarriers
+//   warps 2-5  epilogue: read the accumulator from tensor memory (one corpus row per
+//              thread, 128 scores), compare with each query's running threshold and
+//              append the few survivors to that query's candidate list; two accumulator
+//              buffers let the next tile's MMAs run meanwhile
+// A CTA owns one tile of 128 queries and every ns-th corpus tile; the CTAs of one query
+// tile split the corpus between them and their lists are merged by k_merge_lists.
+//
+// Every wait (mbarrier or otherwise) is bounded by a clock; when one runs out the CTA
+// raises the error word, all roles leave their loops, tensor memory is freed and the
+// host reports LK_ETIMEOUT.  No load is multicast; every GPU reads only its own memory.
+#include <cuda.h>
+
+#include <algorithm>
+#include <string>
+
+#include "../../include/lokiscan.h"
+#include "gemm.cuh"
+#include "lk_common.cuh"
+#include "scan.cuh"
+
+namespace lk {
+
+constexpr int GM = 128;            // corpus rows per tile (MMA M, tensor-memory lanes)
+constexpr int GN = 128;            // queries per tile (MMA N, tensor-memory columns)
+constexpr int GSLICE = 128;        // K bytes per shared-memory slice: one swizzle row
+constexpr int GSLICE_BYTES = GM * GSLICE;  // 16 KB: one slice of a 128-row tile
+constexpr int GCAP = 1024;         // candidate keys a query can hold between prunes
+constexpr int GLIMIT = GCAP - GM;  // prune above this: one tile adds at most 128 per query
+constexpr int GTHREADS = 192;
+constexpr long long GWAIT_CLOCKS = 4000000000ll;  // ~2 s at 2 GHz
+
+__device__ __forceinline__ unsigned g_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void g_mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(g_smem(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void g_mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(g_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void g_mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(g_smem(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the clock ran out or
+// another role of this CTA has already given up.
+__device__ __forceinline__ bool g_mbar_wait(unsigned long long *bar, unsigned parity, volatile int *cta_failed) {
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(g_smem(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (*cta_failed != 0 || clock64() - t0 > GWAIT_CLOCKS) {
+            *cta_failed = 1;
+            return false;
+        }
+    }
+}
+// 2-D tiled TMA load: box at (x = byte column, y = row) of the tensor map -> shared memory
+__device__ __forceinline__ void g_tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, unsigned long long *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            g_smem(dst)),
+        "l"(reinterpret_cast<unsigned long long>(tm)), "r"(x), "r"(y), "r"(g_smem(bar))
+        : "memory");
+}
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ unsigned long long g_smem_desc(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3ffffu) >> 4);        // start address
+    d |= (unsigned long long)1 << 16;                          // leading byte offset (unused with swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (unsigned long long)1 << 46;                          // descriptor version
+    d |= (unsigned long long)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: int8 x int8 (both signed, K-major) -> int32, M = 128, N = 128.
+constexpr unsigned G_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(GN >> 3) << 17) | ((unsigned)(GM >> 4) << 24);
+
+__device__ __forceinline__ void g_mma_i8(unsigned tmem_d, unsigned long long da, unsigned long long db, bool accumulate) {
+    const unsigned acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(da), "l"(db), "r"(G_IDESC), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void g_mma_commit(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(g_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void g_tmem_ld32(unsigned taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Which query tile and which share of the corpus tiles a CTA owns: `grid` CTAs are dealt
+// out to `qtiles` query tiles as evenly as possible (the first grid % qtiles tiles get one more).
+__host__ __device__ inline void gemm_assign(int cta, int grid, int qtiles, int *qt, int *slice, int *nslices) {
+    const int base = grid / qtiles, rem = grid % qtiles;
+    if (cta < rem * (base + 1)) {
+        *qt = cta / (base + 1);
+        *slice = cta % (base + 1);
+        *nslices = base + 1;
+    } else {
+        const int c = cta - rem * (base + 1);
+        *qt = rem + c / base;
+        *slice = c % base;
+        *nslices = base;
+    }
+}
+
+struct GemmShared {  // control words behind the data regions
+    unsigned long long full[8], empty[8], b_full, tmem_full[2], tmem_empty[2];
+    unsigned long long thr[GN];  // per query: keys must exceed this to enter its list
+    int cnt[GN];                 // per query: keys in its list
+    unsigned tmem_base;
+    int need_prune;
+    int failed;           // any role gave up waiting
+    int epilogue_failed;  // written by epilogue threads only (their common exit decision)
+};
+
+// Sort n (<= GCAP) keys of one query in this warp's scratch, descending; n padded to a power of two.
+__device__ inline void g_warp_sort_desc(unsigned long long *s, int sz, int lane) {
+    for (int size = 2; size <= sz; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = lane; i < (sz >> 1); i += 32) {
+                const int pos = 2 * i - (i & (stride - 1));
+                const unsigned long long x = s[pos], y = s[pos + stride];
+                const bool desc = (pos & size) == 0;
+                if ((x < y) == desc) {
+                    s[pos] = y;
+                    s[pos + stride] = x;
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// Keep the best k keys of query q's list (global memory) and raise its threshold.
+__device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q, unsigned long long *scratch, int q,
+                                     int k, int lane) {
+    const int n = min(ctl->cnt[q], GCAP);
+    int sz = 2;
+    while (sz < n) sz <<= 1;
+    for (int i = lane; i < sz; i += 32) scratch[i] = (i < n) ? __ldcg(cand_q + i) : 0ull;
+    __syncwarp();
+    g_warp_sort_desc(scratch, sz, lane);
+    const int keep = min(n, k);
+    for (int i = lane; i < keep; i += 32) __stcg(cand_q + i, scratch[i]);
+    __syncwarp();
+    if (lane == 0) {
+        ctl->cnt[q] = keep;
+        if (keep == k && scratch[k - 1] > ctl->thr[q]) ctl->thr[q] = scratch[k - 1];
+    }
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(GTHREADS, 1)
+k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constant__ CUtensorMap tm_queries,
+               const GemmArgs a) {
+    extern __shared__ unsigned char g_raw[];
+    // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address
+    unsigned char *smem = g_raw + ((1024u - (g_smem(g_raw) & 1023u)) & 1023u);
+    unsigned char *sm_b = smem;                                        // [ks][128 queries][128 B]
+    unsigned char *sm_a = sm_b + (size_t)a.ks * GSLICE_BYTES;          // [stages][128 rows][128 B]
+    unsigned long long *sm_scratch = reinterpret_cast<unsigned long long *>(sm_a + (size_t)a.stages * GSLICE_BYTES);
+    GemmShared *ctl = reinterpret_cast<GemmShared *>(sm_scratch + 4 * GCAP);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int qt, slice, nslices;
+    gemm_assign((int)blockIdx.x, (int)gridDim.x, a.qtiles, &qt, &slice, &nslices);
+    qt += a.qtile0;
+    const long long n_tiles = (a.n + GM - 1) / GM;
+    const int q0 = qt * GN;  // first query of this CTA's tile
+
+    if (tid == 0) {
+        for (int i = 0; i < a.stages; ++i) {
+            g_mbar_init(&ctl->full[i], 1);
+            g_mbar_init(&ctl->empty[i], 1);
+        }
+        g_mbar_init(&ctl->b_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            g_mbar_init(&ctl->tmem_full[i], 1);
+            g_mbar_init(&ctl->tmem_empty[i], 4);  // one arrival per epilogue warp
+        }
+        ctl->need_prune = 0;
+        ctl->failed = 0;
+        ctl->epilogue_failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < GN) {
+        ctl->thr[tid] = (q0 + tid < a.nq) ? 0ull : ~0ull;  // queries past the end accept nothing
+        ctl->cnt[tid] = 0;
+    }
+    if (warp == 1) {  // tensor memory: 2 accumulators x 128 columns
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(g_smem(&ctl->tmem_base)),
+                     "r"(2 * GN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = ctl->tmem_base;
+    volatile int *failed = &ctl->failed;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            g_mbar_expect_tx(&ctl->b_full, (unsigned)(a.ks * GSLICE_BYTES));
+            for (int s = 0; s < a.ks; ++s)
+                g_tma_load_2d(sm_b + (size_t)s * GSLICE_BYTES, &tm_queries, s * GSLICE, q0, &ctl->b_full);
+            int stage = 0;
+            unsigned phase = 0;
+            for (long long t = slice; t < n_tiles && !*failed; t += nslices) {
+                for (int s = 0; s < a.ks; ++s) {
+                    if (!g_mbar_wait(&ctl->empty[stage], phase ^ 1u, failed)) break;
+                    g_mbar_expect_tx(&ctl->full[stage], (unsigned)GSLICE_BYTES);
+                    g_tma_load_2d(sm_a + (size_t)stage * GSLICE_BYTES, &tm_rows, s * GSLICE, (int)(t * GM),
+                                  &ctl->full[stage]);
+                    if (++stage == a.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            bool ok = g_mbar_wait(&ctl->b_full, 0u, failed);
+            int stage = 0, acc = 0;
+            unsigned phase = 0, acc_phase = 0;
+            for (long long t = slice; ok && t < n_tiles; t += nslices) {
+                ok = g_mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, failed);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned d = tmem_base + (unsigned)(acc * GN);
+                for (int s = 0; s < a.ks && ok; ++s) {
+                    ok = g_mbar_wait(&ctl->full[stage], phase, failed);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned long long da = g_smem_desc(g_smem(sm_a + (size_t)stage * GSLICE_BYTES));
+                    const unsigned long long db = g_smem_desc(g_smem(sm_b + (size_t)s * GSLICE_BYTES));
+#pragma unroll
+                    for (int k4 = 0; k4 < GSLICE / 32; ++k4)  // 32 K-bytes per MMA: +2 in 16-byte units
+                        g_mma_i8(d, da + (unsigned long long)(2 * k4), db + (unsigned long long)(2 * k4), (s | k4) != 0);
+                    g_mma_commit(&ctl->empty[stage]);  // the stage is free once these MMAs have read it
+                    if (++stage == a.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                g_mma_commit(&ctl->tmem_full[acc]);  // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int ew = warp - 2;       // 0..3: which queries this warp prunes
+        const int quad = warp & 3;     // tensor-memory lanes this warp may read: 32*quad ..
+        const int etid = ew * 32 + lane;
+        unsigned long long *cand = a.cand + (size_t)blockIdx.x * GN * GCAP;
+        unsigned long long *scratch = sm_scratch + (size_t)ew * GCAP;
+        int acc = 0;
+        unsigned acc_phase = 0;
+        bool ok = true;
+        for (long long t = slice; t < n_tiles; t += nslices) {
+            // all 128 epilogue threads must take the same exit: vote through a word only they write
+            if (!g_mbar_wait(&ctl->tmem_full[acc], acc_phase, failed)) ctl->epilogue_failed = 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            ok = ctl->epilogue_failed == 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const long long row = t * GM + quad * 32 + lane;
+            const bool valid = row < a.n;
+#pragma unroll 1
+            for (int c0 = 0; c0 < GN; c0 += 32) {
+                int v[32];
+                g_tmem_ld32(tmem_base + (unsigned)(acc * GN + c0) + ((unsigned)(quad * 32) << 16), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int q = c0 + j;
+                        const unsigned long long key = make_key(ord_from_i32(v[j]), (unsigned)row);
+                        if (key > ctl->thr[q]) {
+                            const int pos = atomicAdd(&ctl->cnt[q], 1);
+                            if (pos < GCAP) __stcg(cand + (size_t)q * GCAP + pos, key);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) g_mbar_arrive(&ctl->tmem_empty[acc]);
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+            // lists that could overflow on the next tile are pruned now (all four warps take part)
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ctl->cnt[etid] > GLIMIT) ctl->need_prune = 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ctl->need_prune) {
+                __threadfence();
+                for (int q = ew; q < GN; q += 4)
+                    if (ctl->cnt[q] > GLIMIT) g_prune_query(ctl, cand + (size_t)q * GCAP, scratch, q, a.k, lane);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) ctl->need_prune = 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        }
+        // final lists of this CTA: [slice][query][k]
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        __threadfence();
+        for (int q = ew; q < GN; q += 4) {
+            if (q0 + q >= a.nq) continue;
+            g_prune_query(ctl, cand + (size_t)q * GCAP, scratch, q, a.k, lane);
+            const int keep = ok ? ctl->cnt[q] : 0;
+            unsigned long long *dst = a.lists + ((size_t)slice * a.nq + (q0 + q)) * a.k;
+            for (int i = lane; i < a.k; i += 32) dst[i] = (i < keep) ? scratch[i] : 0ull;
+            __syncwarp();
+        }
+    }
+    // ------------------------------ teardown ------------------------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && ctl->failed != 0 && a.error != nullptr) atomicExch(a.error, 1);
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * GN) : "memory");
+    }
+}
+
+}  // namespace lk
+
+namespace lk {
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_fn get_encode() {
+    static encode_fn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_fn>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// [rows x ld bytes] row-major int8 matrix, boxes of 128 rows x 128 bytes, 128-byte swizzle;
+// out-of-range rows and columns read as zero.
+static int make_map(CUtensorMap *tm, const void *base, long long rows, long long ld) {
+    encode_fn enc = get_encode();
+    if (!enc) return fail(LK_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)std::max<long long>(rows, 1)};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld};
+    const cuuint32_t box[2] = {(cuuint32_t)GSLICE, (cuuint32_t)GM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LK_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return 0;
+}
+
+bool gemm_supported(long long ld, int k) { return ld % 16 == 0 && ld <= 1536 && k >= 1 && k <= GEMM_MAX_K; }
+
+size_t gemm_cand_bytes(int grid) { return (size_t)grid * GN * GCAP * 8; }
+
+int gemm_max_slices(int grid, int nq) {
+    const int qtiles = (nq + GN - 1) / GN;
+    const int per_launch = std::min(qtiles, grid);
+    return grid / per_launch + (grid % per_launch ? 1 : 0);
+}
+
+// Enqueue the batched search: lists[slice][nq][k] receives every CTA's ranked keys.
+int gemm_launch(const unsigned char *d_rows, long long n, long long ld, const unsigned char *d_queries, int nq, int k,
+                unsigned long long *d_cand, unsigned long long *d_lists, int *d_error, int sm_count,
+                cudaStream_t stream, long long *launches) {
+    CUtensorMap tm_rows, tm_q;
+    LK_TRY(make_map(&tm_rows, d_rows, n, ld));
+    LK_TRY(make_map(&tm_q, d_queries, nq, ld));
+    const int ks = (int)((ld + GSLICE - 1) / GSLICE);
+    const size_t fixed = (size_t)ks * GSLICE_BYTES + 4 * GCAP * 8 + sizeof(GemmShared) + 1024;
+    int stages = (int)((220 * 1024 - fixed) / GSLICE_BYTES);
+    stages = std::min(stages, 6);
+    if (stages < 2) return fail(LK_ERANGE, "gemm search: rows too wide for the resident query tile");
+    const size_t smem = fixed + (size_t)stages * GSLICE_BYTES;
+    cudaError_t e = cudaFuncSetAttribute((const void *)k_gemm_i8_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(LK_ECUDA, std::string("gemm attr: ") + cudaGetErrorString(e));
+    const int qtiles = (nq + GN - 1) / GN;
+    for (int qt0 = 0; qt0 < qtiles; qt0 += sm_count) {  // at most one query tile per CTA and launch
+        GemmArgs a;
+        a.n = n;
+        a.nq = nq;
+        a.ks = ks;
+        a.stages = stages;
+        a.k = k;
+        a.qtile0 = qt0;
+        a.qtiles = std::min(qtiles - qt0, sm_count);
+        a.cand = d_cand;
+        a.lists = d_lists;
+        a.error = d_error;
+        k_gemm_i8_topk<<<sm_count, GTHREADS, smem, stream>>>(tm_rows, tm_q, a);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(LK_ECUDA, std::string("gemm launch: ") + cudaGetErrorString(e));
+        if (launches) ++*launches;
+    }
+    return 0;
+}
+
+}  // namespace lk

@@ -20,6 +20,7 @@
 #include "../../include/lokiscan.h"
 #include "build.cuh"
 #include "comm.hpp"
+#include "gemm.cuh"
 #include "hostmath.hpp"
 #include "index_internal.cuh"
 #include "lk_common.cuh"
@@ -225,6 +226,65 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
     return 0;
 }
 
+static int unpack_results(const ResultArena &res, int nq, int k_user, int k_eff, int passes, int64_t *out_ids,
+                          float *out_scores, int32_t *out_iscores, int32_t *out_counts);
+
+// A batch of queries against an int8 index as one tensor-core matrix product with the
+// top-k fused into its epilogue (gemm_i8.cu); same scores and ranking as query-by-query scans.
+static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, int k_eff, int64_t *out_ids,
+                       float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+    const int slices = gemm_max_slices(idx->sm_count, nq);
+    const size_t e = (size_t)nq * k_eff;
+    // device: queries | query scales | list bases (zeros) | lists [slices][nq][k] | merge scratch
+    const size_t q_bytes = (size_t)round_up((int64_t)nq * idx->qbytes, 256);
+    const size_t qs_bytes = (size_t)round_up((int64_t)nq * 4, 256);
+    const size_t base_bytes = (size_t)round_up((int64_t)slices * 8, 256);
+    const size_t list_bytes = (size_t)slices * e * 8;
+    LK_TRY(idx->h_query.reserve(q_bytes + qs_bytes));
+    LK_TRY(idx->d_query.reserve(q_bytes + qs_bytes + base_bytes + 2 * list_bytes));
+    LK_TRY(idx->gemm_cand.reserve(gemm_cand_bytes(idx->sm_count)));
+    LK_TRY(idx->res.shape(nq, k_eff, 1));
+    unsigned char *hq = (unsigned char *)idx->h_query.p;
+    float *hqs = (float *)(hq + q_bytes);
+    for (int q = 0; q < nq; ++q) {
+        float cq;
+        prepare_query(idx, queries + (size_t)q * idx->dim, LK_SCORE_PLAIN, hq + (size_t)q * idx->qbytes, &cq, &hqs[q]);
+    }
+    unsigned char *dq = (unsigned char *)idx->d_query.p;
+    LK_CUDA(cudaMemcpyAsync(dq, hq, q_bytes + qs_bytes, cudaMemcpyHostToDevice, idx->stream));
+    LK_CUDA(cudaMemsetAsync(dq + q_bytes + qs_bytes, 0, base_bytes + list_bytes, idx->stream));
+    unsigned long long *d_lists = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes);
+    int *d_err = (int *)(idx->d_ticket + 1);
+    LK_TRY(gemm_launch(idx->d_rows, idx->len, idx->ld, dq, nq, k_eff, (unsigned long long *)idx->gemm_cand.p, d_lists,
+                       d_err, idx->sm_count, idx->stream, &idx->aux_launches));
+    MergeArgs m;
+    m.keys = d_lists;
+    m.payload = nullptr;
+    m.qscales = (const float *)(dq + q_bytes);
+    m.scales = idx->d_scales;
+    m.scratch = d_lists + (size_t)slices * e;
+    m.list_base = (const long long *)(dq + q_bytes + qs_bytes);
+    m.lists = slices;
+    m.nq = nq;
+    m.k = k_eff;
+    m.type = SCAN_I8;
+    m.out_ids = idx->res.d_ids();
+    m.out_scores = idx->res.d_scores();
+    m.out_iscores = idx->res.d_iscores();
+    m.out_count = idx->res.d_counts();
+    LK_TRY(merge_launch(m, idx->stream));
+    idx->aux_launches++;
+    int h_err = 0;
+    LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaMemcpyAsync(&h_err, d_err, 4, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    if (h_err != 0) {
+        LK_CUDA(cudaMemsetAsync(d_err, 0, 4, idx->stream));
+        return fail(LK_ETIMEOUT, "the batched search kernel gave up on a bounded wait; results are not valid");
+    }
+    return unpack_results(idx->res, nq, k_user, k_eff, 1, out_ids, out_scores, out_iscores, out_counts);
+}
+
 // Lowest-latency form of a single query: the prepared query rides in the launch
 // parameters (no upload), the kernel writes the k results straight into mapped pinned
 // host memory and releases a flag the host is polling (no download, no stream sync).
@@ -387,6 +447,7 @@ int lk_index_destroy(lk_index *idx) {
     idx->d_stage.release();
     idx->h_query.release();
     idx->zc.release();
+    idx->gemm_cand.release();
     idx->gather.release();
     if (idx->ev0) cudaEventDestroy(idx->ev0);
     if (idx->ev1) cudaEventDestroy(idx->ev1);
@@ -512,6 +573,12 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     const int k_eff = sharded ? k : (int)std::min<long long>(k, n_cand);
     const int passes = (k_eff + kMaxK - 1) / kMaxK;
     if (sharded && passes > 1) return fail(LK_ERANGE, "lk_search: k above the single-pass limit is not supported on a sharded index");
+    if (idx->store == LK_I8 && nq >= GEMM_MIN_QUERIES && !filtered && !sharded && gemm_supported(idx->ld, k_eff) &&
+        idx->len >= 4096 && !idx->no_gemm) {
+        LK_TRY(search_gemm(idx, queries, nq, k, k_eff, out_ids, out_scores, out_iscores, out_counts));
+        idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        return LK_OK;
+    }
     LK_TRY(ensure_scan_scratch(idx, std::min(k_eff, kMaxK)));
     const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
     if (nq == 1 && passes == 1 && k_eff <= kFastMaxK && idx->qbytes <= kInlineQueryBytes && (!sharded || peer)) {
@@ -762,6 +829,12 @@ int lk_index_sync(lk_index *idx) {
     if (!idx) return fail(LK_EINVAL, "lk_index_sync: idx is NULL");
     LK_TRY(use_device(idx));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
+    return LK_OK;
+}
+
+int lk_index_set_batch_mode(lk_index *idx, int mode) {
+    if (!idx || (mode != 0 && mode != 1)) return fail(LK_EINVAL, "lk_index_set_batch_mode: bad argument");
+    idx->no_gemm = (mode == 0);
     return LK_OK;
 }
 

@@ -131,6 +131,8 @@ struct lk_index {
     lk::PinnedBuf h_query;
     lk::PinnedBuf zc;           // mapped pinned block the kernel writes single-query results into
     unsigned int zc_seq = 0;
+    lk::DevBuf gemm_cand;       // candidate lists of the batched tensor-core search
+    bool no_gemm = false;       // batches run as single-query scans (lk_index_set_batch_mode)
     // multi-GPU
     lk_comm *comm = nullptr;
     long long shard_base = 0;

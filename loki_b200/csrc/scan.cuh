@@ -97,6 +97,8 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
 struct MergeArgs {
     const unsigned long long *keys;  // [lists][nq][k] ranked descending, ids local to each list
     const float *payload;            // [lists][nq][k] finished float score of each int8 hit, else nullptr
+    const float *qscales;            // int8 without payload: per-query scale ...
+    const float *scales;             // ... and per-row scale (rows local to this GPU), to finish the float score here
     unsigned long long *scratch;     // [nq][lists*k] work space
     const long long *list_base;      // [lists] ascending id offset of each list (device)
     int lists;

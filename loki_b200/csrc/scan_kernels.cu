@@ -989,6 +989,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_merge_lists(const MergeArgs
             if (out_iscores) out_iscores[i] = 0;
             continue;
         }
+        if (a.payload == nullptr) {  // single GPU: the row scales are here
+            const int isc = i32_from_ord(key_ord(key));
+            out_scores[i] = (float)isc * (a.qscales[q] * a.scales[gid]);
+            if (out_iscores) out_iscores[i] = isc;
+            continue;
+        }
         // int8: the float score was finished by the shard that owns the row (it needs
         // the row's scale); find the key in its origin list (ranked descending).
         int l = 0;
