@@ -234,6 +234,20 @@ LK_API int lk_scan_i8_prealloc(int device, const int8_t *d_codes, int64_t n, int
                                int64_t *d_out_ids, float *d_out_scores, int32_t *d_out_iscores,
                                int32_t *d_out_count, void *stream);
 
+/* ---- face-clustering neighbour prescreen ------------------------------------ */
+
+/* Replaces prescreenCandidates (media-server/tasks/face_cluster.go:1189-1285): for every
+ * vector i (n unit vectors of dim floats, row-major, in processing order) the earlier
+ * vectors j < i with dotf(v_i, v_j) >= threshold (media-server/tasks/face_cluster.go:908-925:
+ * float32, four interleaved accumulators), ascending.
+ *   near      n x LK_PRESCREEN_MAX int32: row i holds count[i] neighbour positions
+ *   count     n int32
+ *   overflow  n bytes: 1 = more than LK_PRESCREEN_MAX neighbours, list dropped (count 0),
+ *             exactly the reference's overflow rule */
+#define LK_PRESCREEN_MAX 256
+LK_API int lk_prescreen_pairs(const float *vecs, int64_t n, int dim, float threshold, int device,
+                              int32_t *near, int32_t *count, uint8_t *overflow);
+
 /* ---- statistics ----------------------------------------------------------- */
 
 typedef struct {

@@ -17,7 +17,7 @@ except Exception:  # pragma: no cover - torch is optional for this package
     torch = None
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblokiscan.so")
+LIB_PATH = os.environ.get("LOKI_B200_LIB", os.path.join(_HERE, "liblokiscan.so"))  # override: tuning builds only
 
 LK_OK, LK_EINVAL, LK_EDIM, LK_ENOMEM, LK_ECUDA, LK_ENCCL, LK_ETIMEOUT, LK_ERANGE = range(8)
 LK_F32, LK_F16, LK_I8 = 0, 1, 2
@@ -93,6 +93,7 @@ _sig("lk_hamming_pairs", _int, _vp, _i64, _int, _int, _int, _int, _vp, _i64, C.P
 _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64, C.POINTER(_i64))
 _sig("lk_stats", _int, _vp, C.POINTER(lk_stats_t))
 _sig("lk_index_set_batch_mode", _int, _vp, _int)
+_sig("lk_prescreen_pairs", _int, _vp, _i64, _int, C.c_float, _int, _vp, _vp, _vp)
 _sig("lk_scan_i8_prealloc", _int, _int, _vp, _i64, _int, _i64, _vp, _vp, C.c_float, _int, _vp, _vp, _vp, _vp, _vp)
 LK_PREALLOC_MAX_K = 128
 
@@ -341,3 +342,14 @@ def hamming_scan(hashes, query: int, radius: int, cap: int | None = None, device
                               ptr(ids), ptr(dist), int(cap), C.byref(cnt)))
     n = min(cnt.value, cap)
     return ids[:n].copy(), dist[:n].copy(), int(cnt.value)
+
+
+def prescreen_pairs(vecs, threshold: float, device: int = 0):
+    """Neighbour prescreen of face clustering: -> (near[n,256] int32, count[n], overflow[n] bool)."""
+    v = np.ascontiguousarray(vecs, dtype=np.float32)
+    n, dim = v.shape
+    near = np.zeros((max(n, 1), 256), np.int32)
+    count = np.zeros(max(n, 1), np.int32)
+    over = np.zeros(max(n, 1), np.uint8)
+    check(lib.lk_prescreen_pairs(ptr(v), n, dim, C.c_float(threshold), int(device), ptr(near), ptr(count), ptr(over)))
+    return near[:n], count[:n], over[:n].astype(bool)

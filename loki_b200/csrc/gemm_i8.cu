@@ -9,15 +9,15 @@
 // int32 dots of the single-query scan, and ranking uses the same 64-bit keys, so the
 // result is bit-identical to running the queries one by one.
 //
-// Shape of one CTA (192 threads, one CTA per SM):
+// Shape of one CTA (320 threads, one CTA per SM):
 //   warp 0     TMA producer: 2-D tiled loads (128-byte swizzle) of corpus tiles
 //              [128 rows x 128 K-bytes] into a ring of stages; loads the CTA's query
 //              tile [128 queries x all K] once, it stays resident in shared memory
 //   warp 1     allocates tensor memory and issues the MMAs: D[128 rows x 128 queries]
 //              += A[128 x 32] * B[128 x 32]^T, four per 128-byte K slice; commits free
 //              the stage / publish the accumulator through mbarriers
-//   warps 2-5  epilogue: read the accumulator from tensor memory (one corpus row per
-//              thread, 128 scores), compare with each query's running threshold and
+//   warps 2-9  epilogue: read the accumulator from tensor memory (one corpus row and 64
+//              queries per thread), compare with each query's running threshold and
 //              append the few survivors to that query's candidate list; two accumulator
 //              buffers let the next tile's MMAs run meanwhile
 // A CTA owns one tile of 128 queries and every ns-th corpus tile; the CTAs of one query
@@ -42,9 +42,17 @@ constexpr int GM = 128;            // corpus rows per tile (MMA M, tensor-memory
 constexpr int GN = 128;            // queries per tile (MMA N, tensor-memory columns)
 constexpr int GSLICE = 128;        // K bytes per shared-memory slice: one swizzle row
 constexpr int GSLICE_BYTES = GM * GSLICE;  // 16 KB: one slice of a 128-row tile
-constexpr int GCAP = 1024;         // candidate keys a query can hold between prunes
-constexpr int GLIMIT = GCAP - GM;  // prune above this: one tile adds at most 128 per query
-constexpr int GTHREADS = 192;
+constexpr int GCAP_MAX = 512;      // most candidate keys a query holds between prunes (k <= 256)
+constexpr int GEPI_WARPS = 8;      // epilogue warps: two per tensor-memory lane quadrant
+constexpr int GEPI_THREADS = GEPI_WARPS * 32;
+constexpr int GTHREADS = 64 + GEPI_THREADS;
+// A query's list holds cap = pow2ceil(k + 128) keys: one tile adds at most 128, so a list
+// is pruned back to k whenever it exceeds cap - 128.  Small lists keep the sorts short.
+__host__ __device__ inline int gemm_cap(int k) {
+    int c = 256;
+    while (c < k + GM) c <<= 1;
+    return c;
+}
 constexpr long long GWAIT_CLOCKS = 4000000000ll;  // ~2 s at 2 GHz
 
 __device__ __forceinline__ unsigned g_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -141,9 +149,19 @@ __host__ __device__ inline void gemm_assign(int cta, int grid, int qtiles, int *
     }
 }
 
+#ifdef LK_GEMM_PROFILE
+__device__ unsigned long long g_gemm_prof[16];  // summed clocks per role and phase (tuning builds only)
+#define GPROF_T0 const long long _pt0 = clock64()
+#define GPROF_ADD(i) atomicAdd(&g_gemm_prof[i], (unsigned long long)(clock64() - _pt0))
+#else
+#define GPROF_T0
+#define GPROF_ADD(i)
+#endif
+
 struct GemmShared {  // control words behind the data regions
     unsigned long long full[8], empty[8], b_full, tmem_full[2], tmem_empty[2];
     unsigned long long thr[GN];  // per query: keys must exceed this to enter its list
+    alignas(16) int thr_score[GN];  // score part of thr: the cheap first test (score >= thr_score)
     int cnt[GN];                 // per query: keys in its list
     unsigned tmem_base;
     int need_prune;
@@ -151,7 +169,7 @@ struct GemmShared {  // control words behind the data regions
     int epilogue_failed;  // written by epilogue threads only (their common exit decision)
 };
 
-// Sort n (<= GCAP) keys of one query in this warp's scratch, descending; n padded to a power of two.
+// Sort n (<= cap) keys of one query in this warp's scratch, descending; n padded to a power of two.
 __device__ inline void g_warp_sort_desc(unsigned long long *s, int sz, int lane) {
     for (int size = 2; size <= sz; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -171,11 +189,23 @@ __device__ inline void g_warp_sort_desc(unsigned long long *s, int sz, int lane)
 
 // Keep the best k keys of query q's list (global memory) and raise its threshold.
 __device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q, unsigned long long *scratch, int q,
-                                     int k, int lane) {
-    const int n = min(ctl->cnt[q], GCAP);
+                                     int k, int cap, int lane) {
+    const int n = min(ctl->cnt[q], cap);
     int sz = 2;
     while (sz < n) sz <<= 1;
-    for (int i = lane; i < sz; i += 32) scratch[i] = (i < n) ? __ldcg(cand_q + i) : 0ull;
+    {
+        unsigned long long r[GCAP_MAX / 32];  // all loads in flight at once
+#pragma unroll
+        for (int u = 0; u < GCAP_MAX / 32; ++u) {
+            const int i = lane + 32 * u;
+            r[u] = (i < n) ? __ldcg(cand_q + i) : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < GCAP_MAX / 32; ++u) {
+            const int i = lane + 32 * u;
+            if (i < sz) scratch[i] = r[u];
+        }
+    }
     __syncwarp();
     g_warp_sort_desc(scratch, sz, lane);
     const int keep = min(n, k);
@@ -183,7 +213,10 @@ __device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q
     __syncwarp();
     if (lane == 0) {
         ctl->cnt[q] = keep;
-        if (keep == k && scratch[k - 1] > ctl->thr[q]) ctl->thr[q] = scratch[k - 1];
+        if (keep == k && scratch[k - 1] > ctl->thr[q]) {
+            ctl->thr[q] = scratch[k - 1];
+            ctl->thr_score[q] = i32_from_ord(key_ord(scratch[k - 1]));
+        }
     }
     __syncwarp();
 }
@@ -197,7 +230,8 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     unsigned char *sm_b = smem;                                        // [ks][128 queries][128 B]
     unsigned char *sm_a = sm_b + (size_t)a.ks * GSLICE_BYTES;          // [stages][128 rows][128 B]
     unsigned long long *sm_scratch = reinterpret_cast<unsigned long long *>(sm_a + (size_t)a.stages * GSLICE_BYTES);
-    GemmShared *ctl = reinterpret_cast<GemmShared *>(sm_scratch + 4 * GCAP);
+    const int cap = gemm_cap(a.k), limit = cap - GM;
+    GemmShared *ctl = reinterpret_cast<GemmShared *>(sm_scratch + (size_t)GEPI_WARPS * cap);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int qt, slice, nslices;
@@ -214,7 +248,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
         g_mbar_init(&ctl->b_full, 1);
         for (int i = 0; i < 2; ++i) {
             g_mbar_init(&ctl->tmem_full[i], 1);
-            g_mbar_init(&ctl->tmem_empty[i], 4);  // one arrival per epilogue warp
+            g_mbar_init(&ctl->tmem_empty[i], GEPI_WARPS);  // one arrival per epilogue warp
         }
         ctl->need_prune = 0;
         ctl->failed = 0;
@@ -222,7 +256,9 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < GN) {
-        ctl->thr[tid] = (q0 + tid < a.nq) ? 0ull : ~0ull;  // queries past the end accept nothing
+        const bool live = q0 + tid < a.nq;  // queries past the end accept nothing
+        ctl->thr[tid] = live ? 0ull : ~0ull;
+        ctl->thr_score[tid] = live ? (int)0x80000000 : 0x7fffffff;
         ctl->cnt[tid] = 0;
     }
     if (warp == 1) {  // tensor memory: 2 accumulators x 128 columns
@@ -248,7 +284,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
             unsigned phase = 0;
             for (long long t = slice; t < n_tiles && !*failed; t += nslices) {
                 for (int s = 0; s < a.ks; ++s) {
-                    if (!g_mbar_wait(&ctl->empty[stage], phase ^ 1u, failed)) break;
+                    { GPROF_T0; const bool w = g_mbar_wait(&ctl->empty[stage], phase ^ 1u, failed); GPROF_ADD(0); if (!w) break; }
                     g_mbar_expect_tx(&ctl->full[stage], (unsigned)GSLICE_BYTES);
                     g_tma_load_2d(sm_a + (size_t)stage * GSLICE_BYTES, &tm_rows, s * GSLICE, (int)(t * GM),
                                   &ctl->full[stage]);
@@ -266,12 +302,12 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
             int stage = 0, acc = 0;
             unsigned phase = 0, acc_phase = 0;
             for (long long t = slice; ok && t < n_tiles; t += nslices) {
-                ok = g_mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, failed);
+                { GPROF_T0; ok = g_mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, failed); GPROF_ADD(1); }
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned d = tmem_base + (unsigned)(acc * GN);
                 for (int s = 0; s < a.ks && ok; ++s) {
-                    ok = g_mbar_wait(&ctl->full[stage], phase, failed);
+                    { GPROF_T0; ok = g_mbar_wait(&ctl->full[stage], phase, failed); GPROF_ADD(2); }
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned long long da = g_smem_desc(g_smem(sm_a + (size_t)stage * GSLICE_BYTES));
@@ -295,66 +331,90 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        const int ew = warp - 2;       // 0..3: which queries this warp prunes
-        const int quad = warp & 3;     // tensor-memory lanes this warp may read: 32*quad ..
+        // 8 warps: warp w reads tensor-memory lanes 32*(w%4).. (the hardware's rule) and the
+        // column half (w-2)/4, i.e. one corpus row x 64 queries per thread and tile.
+        const int ew = warp - 2;       // 0..7
+        const int quad = warp & 3;
+        const int half = ew >> 2;
         const int etid = ew * 32 + lane;
-        unsigned long long *cand = a.cand + (size_t)blockIdx.x * GN * GCAP;
-        unsigned long long *scratch = sm_scratch + (size_t)ew * GCAP;
+        unsigned long long *cand = a.cand + (size_t)blockIdx.x * GN * GCAP_MAX;
+        unsigned long long *scratch = sm_scratch + (size_t)ew * cap;
         int acc = 0;
         unsigned acc_phase = 0;
         bool ok = true;
         for (long long t = slice; t < n_tiles; t += nslices) {
-            // all 128 epilogue threads must take the same exit: vote through a word only they write
-            if (!g_mbar_wait(&ctl->tmem_full[acc], acc_phase, failed)) ctl->epilogue_failed = 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // all epilogue threads must take the same exit: vote through a word only they write
+            { GPROF_T0; if (!g_mbar_wait(&ctl->tmem_full[acc], acc_phase, failed)) ctl->epilogue_failed = 1; if (etid == 0) GPROF_ADD(3); }
+            GPROF_T0;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             ok = ctl->epilogue_failed == 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long row = t * GM + quad * 32 + lane;
             const bool valid = row < a.n;
 #pragma unroll 1
-            for (int c0 = 0; c0 < GN; c0 += 32) {
+            for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
                 int v[32];
                 g_tmem_ld32(tmem_base + (unsigned)(acc * GN + c0) + ((unsigned)(quad * 32) << 16), v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (valid) {
+                // the 32 score thresholds of these queries, while the load is in flight
+                int ts[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int q = c0 + j;
-                        const unsigned long long key = make_key(ord_from_i32(v[j]), (unsigned)row);
-                        if (key > ctl->thr[q]) {
-                            const int pos = atomicAdd(&ctl->cnt[q], 1);
-                            if (pos < GCAP) __stcg(cand + (size_t)q * GCAP + pos, key);
-                        }
+                for (int j = 0; j < 32; j += 4) {
+                    const int4 w = *reinterpret_cast<const int4 *>(&ctl->thr_score[c0 + j]);
+                    ts[j] = w.x; ts[j + 1] = w.y; ts[j + 2] = w.z; ts[j + 3] = w.w;
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                unsigned pass = 0;  // branch-free first test: one bit per query of the chunk
+#pragma unroll
+                for (int j = 0; j < 32; ++j) pass |= (v[j] >= ts[j] ? 1u : 0u) << j;
+                if (!valid) pass = 0;
+                while (pass) {  // rare once the thresholds have risen
+                    const int j = __ffs(pass) - 1;
+                    pass &= pass - 1;
+                    int sv = 0;
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj)
+                        if (jj == j) sv = v[jj];
+                    const int q = c0 + j;
+                    const unsigned long long key = make_key(ord_from_i32(sv), (unsigned)row);
+                    if (key > ctl->thr[q]) {
+                        const int pos = atomicAdd(&ctl->cnt[q], 1);
+                        if (pos < cap) __stcg(cand + (size_t)q * GCAP_MAX + pos, key);
                     }
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) g_mbar_arrive(&ctl->tmem_empty[acc]);
+            if (etid == 0) GPROF_ADD(4);
             if (++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1u;
             }
-            // lists that could overflow on the next tile are pruned now (all four warps take part)
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (ctl->cnt[etid] > GLIMIT) ctl->need_prune = 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // lists that could overflow on the next tile are pruned now (all warps take part)
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (etid < GN && ctl->cnt[etid] > limit) ctl->need_prune = 1;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (ctl->need_prune) {
+                GPROF_T0;
                 __threadfence();
-                for (int q = ew; q < GN; q += 4)
-                    if (ctl->cnt[q] > GLIMIT) g_prune_query(ctl, cand + (size_t)q * GCAP, scratch, q, a.k, lane);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                // every list above k is pruned, not only the full ones: the queries of a tile fill at
+                // similar rates, so this turns hundreds of one-list stalls into a handful of events
+                // in which all eight warps sort at once
+                for (int q = ew; q < GN; q += GEPI_WARPS)
+                    if (ctl->cnt[q] > a.k) g_prune_query(ctl, cand + (size_t)q * GCAP_MAX, scratch, q, a.k, cap, lane);
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (etid == 0) ctl->need_prune = 0;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (etid == 0) GPROF_ADD(5);
             }
         }
         // final lists of this CTA: [slice][query][k]
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         __threadfence();
-        for (int q = ew; q < GN; q += 4) {
+        for (int q = ew; q < GN; q += GEPI_WARPS) {
             if (q0 + q >= a.nq) continue;
-            g_prune_query(ctl, cand + (size_t)q * GCAP, scratch, q, a.k, lane);
+            g_prune_query(ctl, cand + (size_t)q * GCAP_MAX, scratch, q, a.k, cap, lane);
             const int keep = ok ? ctl->cnt[q] : 0;
             unsigned long long *dst = a.lists + ((size_t)slice * a.nq + (q0 + q)) * a.k;
             for (int i = lane; i < a.k; i += 32) dst[i] = (i < keep) ? scratch[i] : 0ull;
@@ -411,9 +471,19 @@ static int make_map(CUtensorMap *tm, const void *base, long long rows, long long
     return 0;
 }
 
+#ifdef LK_GEMM_PROFILE
+extern "C" __attribute__((visibility("default"))) void lk_debug_gemm_profile(unsigned long long *out16, int reset) {
+    cudaMemcpyFromSymbol(out16, g_gemm_prof, sizeof(unsigned long long) * 16);
+    if (reset) {
+        unsigned long long z[16] = {};
+        cudaMemcpyToSymbol(g_gemm_prof, z, sizeof(z));
+    }
+}
+#endif
+
 bool gemm_supported(long long ld, int k) { return ld % 16 == 0 && ld <= 1536 && k >= 1 && k <= GEMM_MAX_K; }
 
-size_t gemm_cand_bytes(int grid) { return (size_t)grid * GN * GCAP * 8; }
+size_t gemm_cand_bytes(int grid) { return (size_t)grid * GN * GCAP_MAX * 8; }
 
 int gemm_max_slices(int grid, int nq) {
     const int qtiles = (nq + GN - 1) / GN;
@@ -429,7 +499,7 @@ int gemm_launch(const unsigned char *d_rows, long long n, long long ld, const un
     LK_TRY(make_map(&tm_rows, d_rows, n, ld));
     LK_TRY(make_map(&tm_q, d_queries, nq, ld));
     const int ks = (int)((ld + GSLICE - 1) / GSLICE);
-    const size_t fixed = (size_t)ks * GSLICE_BYTES + 4 * GCAP * 8 + sizeof(GemmShared) + 1024;
+    const size_t fixed = (size_t)ks * GSLICE_BYTES + (size_t)GEPI_WARPS * gemm_cap(k) * 8 + sizeof(GemmShared) + 1024;
     int stages = (int)((220 * 1024 - fixed) / GSLICE_BYTES);
     stages = std::min(stages, 6);
     if (stages < 2) return fail(LK_ERANGE, "gemm search: rows too wide for the resident query tile");

@@ -240,18 +240,18 @@ static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, 
     const size_t qs_bytes = (size_t)round_up((int64_t)nq * 4, 256);
     const size_t base_bytes = (size_t)round_up((int64_t)slices * 8, 256);
     const size_t list_bytes = (size_t)slices * e * 8;
-    LK_TRY(idx->h_query.reserve(q_bytes + qs_bytes));
     LK_TRY(idx->d_query.reserve(q_bytes + qs_bytes + base_bytes + 2 * list_bytes));
     LK_TRY(idx->gemm_cand.reserve(gemm_cand_bytes(idx->sm_count)));
     LK_TRY(idx->res.shape(nq, k_eff, 1));
-    unsigned char *hq = (unsigned char *)idx->h_query.p;
-    float *hqs = (float *)(hq + q_bytes);
-    for (int q = 0; q < nq; ++q) {
-        float cq;
-        prepare_query(idx, queries + (size_t)q * idx->dim, LK_SCORE_PLAIN, hq + (size_t)q * idx->qbytes, &cq, &hqs[q]);
-    }
+    // Queries are prepared on the device by the same kernel that stores rows (a query is
+    // normalised and quantised exactly like a row): upload the raw float32 batch, convert.
+    const size_t raw_bytes = (size_t)nq * idx->dim * sizeof(float);
+    LK_TRY(idx->d_stage.reserve(raw_bytes));
     unsigned char *dq = (unsigned char *)idx->d_query.p;
-    LK_CUDA(cudaMemcpyAsync(dq, hq, q_bytes + qs_bytes, cudaMemcpyHostToDevice, idx->stream));
+    LK_CUDA(cudaMemcpyAsync(idx->d_stage.p, queries, raw_bytes, cudaMemcpyHostToDevice, idx->stream));
+    LK_TRY(normalize_store_launch(LK_I8, (const float *)idx->d_stage.p, nq, idx->dim, dq, idx->ld,
+                                  (float *)(dq + q_bytes), idx->sm_count, idx->stream));
+    idx->aux_launches++;
     LK_CUDA(cudaMemsetAsync(dq + q_bytes + qs_bytes, 0, base_bytes + list_bytes, idx->stream));
     unsigned long long *d_lists = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes);
     int *d_err = (int *)(idx->d_ticket + 1);

@@ -92,6 +92,12 @@ def lib():
     L.orc_hamming_pairs.restype = C.c_int64
     L.orc_hamming_scan.argtypes = [_u64p, C.c_int64, C.c_uint64, _i32p]
     L.orc_hamming_scan.restype = None
+    _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+    L.orc_dotf.argtypes = [_f32p, _f32p, C.c_int]
+    L.orc_dotf.restype = C.c_float
+    for fn in (L.orc_prescreen, L.orc_prescreen_bruteforce):
+        fn.argtypes = [_f32p, C.c_int, C.c_int, C.c_float, _i32p, _i32p, _u8p]
+        fn.restype = None
     _lib = L
     return L
 
@@ -298,3 +304,26 @@ class SharedQuery:
         return dict(pos=pos, basis=basis[:self.rank], posw=posw, posnorm=posnorm,
                     qb=qb.reshape(-1)[:self.m * self.rank].reshape(self.m, self.rank) if self.rank else qb[:, :0],
                     gamma=np.float32(g.value))
+
+
+# ---- face-clustering prescreen (media-server/tasks/face_cluster.go:1189-1285) --------
+
+MAX_FORM_CANDIDATES = 256
+
+
+def dotf(a, b) -> np.float32:
+    a, b = _f32(a), _f32(b)
+    return np.float32(lib().orc_dotf(a, b, a.size)) if a.size == b.size else np.float32(0)
+
+
+def prescreen(vecs, threshold: float, brute_force: bool = False):
+    """-> (near[n, 256] int32, count[n] int32, overflow[n] bool) for unit rows `vecs`."""
+    v = _f32(vecs)
+    n, d = v.shape
+    near = np.zeros((max(n, 1), MAX_FORM_CANDIDATES), np.int32)
+    count = np.zeros(max(n, 1), np.int32)
+    over = np.zeros(max(n, 1), np.uint8)
+    fn = lib().orc_prescreen_bruteforce if brute_force else lib().orc_prescreen
+    if n:
+        fn(v, n, d, float(threshold), near.reshape(-1), count, over)
+    return near[:n], count[:n], over[:n].astype(bool)

@@ -468,3 +468,111 @@ ORC_API int64_t orc_hamming_pairs(const uint64_t *h, int64_t n, int radius,
 ORC_API void orc_hamming_scan(const uint64_t *h, int64_t n, uint64_t q, int32_t *dist) {
     for (int64_t i = 0; i < n; i++) dist[i] = __builtin_popcountll(h[i] ^ q);
 }
+
+/* ------------------------------------------------------------------------- */
+/* tasks/face_cluster.go: the all-pairs neighbour prescreen of face clustering  */
+/* ------------------------------------------------------------------------- */
+
+/* float32 dot with four interleaved accumulators, combined (s0+s1)+(s2+s3).
+ * Follows media-server/tasks/face_cluster.go:908-925 (equal lengths assumed). */
+ORC_API float orc_dotf(const float *a, const float *b, int n) {
+    float s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    int i = 0;
+    for (; i + 4 <= n; i += 4) {
+        s0 += a[i] * b[i];
+        s1 += a[i + 1] * b[i + 1];
+        s2 += a[i + 2] * b[i + 2];
+        s3 += a[i + 3] * b[i + 3];
+    }
+    for (; i < n; i++) s0 += a[i] * b[i];
+    return (s0 + s1) + (s2 + s3);
+}
+
+/* b against four rows at once: even elements into s, odd into t, result s + t.
+ * Follows media-server/tasks/face_cluster.go:939-967. */
+static void dot4(const float *a0, const float *a1, const float *a2, const float *a3, const float *b, int n,
+                 float out[4]) {
+    float s0 = 0, s1 = 0, s2 = 0, s3 = 0, t0 = 0, t1 = 0, t2 = 0, t3 = 0;
+    int i = 0;
+    for (; i + 2 <= n; i += 2) {
+        float x = b[i], y = b[i + 1];
+        s0 += a0[i] * x; t0 += a0[i + 1] * y;
+        s1 += a1[i] * x; t1 += a1[i + 1] * y;
+        s2 += a2[i] * x; t2 += a2[i + 1] * y;
+        s3 += a3[i] * x; t3 += a3[i + 1] * y;
+    }
+    for (; i < n; i++) {
+        float x = b[i];
+        s0 += a0[i] * x; s1 += a1[i] * x; s2 += a2[i] * x; s3 += a3[i] * x;
+    }
+    out[0] = s0 + t0; out[1] = s1 + t1; out[2] = s2 + t2; out[3] = s3 + t3;
+}
+
+#define ORC_MAX_FORM 256 /* maxFormCandidates, media-server/tasks/face_cluster.go:1156 */
+
+/* For every row i the earlier rows j < i with dot >= threshold, ascending, at most 256;
+ * a row with more is marked overflow and its list dropped.  near is n x 256 int32,
+ * count n int32, overflow n bytes.  Row tiles of 64, column tiles ascending, four rows at a
+ * time through dot4 off the diagonal, dotf elsewhere: follows
+ * media-server/tasks/face_cluster.go:1189-1285 (the result does not depend on how the
+ * reference's workers interleave: a row tile belongs to one worker). */
+ORC_API void orc_prescreen(const float *v, int n, int d, float threshold, int32_t *near, int32_t *count,
+                           uint8_t *overflow) {
+    const int tile = 64;
+    memset(count, 0, sizeof(int32_t) * (size_t)n);
+    memset(overflow, 0, (size_t)n);
+    /* lists may transiently hold more than 256 entries inside the four-row fast path */
+    int32_t *tmp = (int32_t *)malloc(sizeof(int32_t) * (size_t)n * (ORC_MAX_FORM + tile + 1));
+    const size_t ts = ORC_MAX_FORM + tile + 1;
+    for (int iLo = 0; iLo < n; iLo += tile) {
+        int iHi = iLo + tile < n ? iLo + tile : n;
+        for (int jLo = 0; jLo < iHi; jLo += tile) {
+            int jHi = jLo + tile < iHi ? jLo + tile : iHi;
+            int i = iLo;
+            if (jHi <= iLo) {
+                for (; i + 4 <= iHi; i += 4) {
+                    if (overflow[i] || overflow[i + 1] || overflow[i + 2] || overflow[i + 3]) break;
+                    for (int j = jLo; j < jHi; j++) {
+                        float s[4];
+                        dot4(v + (size_t)i * d, v + (size_t)(i + 1) * d, v + (size_t)(i + 2) * d,
+                             v + (size_t)(i + 3) * d, v + (size_t)j * d, d, s);
+                        for (int r = 0; r < 4; r++)
+                            if (s[r] >= threshold) tmp[(size_t)(i + r) * ts + count[i + r]++] = j;
+                    }
+                    for (int r = i; r < i + 4; r++)
+                        if (count[r] > ORC_MAX_FORM) { overflow[r] = 1; count[r] = 0; }
+                }
+            }
+            for (; i < iHi; i++) {
+                if (overflow[i]) continue;
+                int jEnd = jHi < i ? jHi : i;
+                for (int j = jLo; j < jEnd; j++) {
+                    if (orc_dotf(v + (size_t)i * d, v + (size_t)j * d, d) < threshold) continue;
+                    if (count[i] == ORC_MAX_FORM) { overflow[i] = 1; count[i] = 0; break; }
+                    tmp[(size_t)i * ts + count[i]++] = j;
+                }
+            }
+        }
+    }
+    for (int i = 0; i < n; i++)
+        memcpy(near + (size_t)i * ORC_MAX_FORM, tmp + (size_t)i * ts, sizeof(int32_t) * (size_t)count[i]);
+    free(tmp);
+}
+
+/* The definition the reference's own test checks the prescreen against
+ * (media-server/tasks/face_cluster_perf_test.go:52-81): every j < i with dotf >= threshold. */
+ORC_API void orc_prescreen_bruteforce(const float *v, int n, int d, float threshold, int32_t *near,
+                                      int32_t *count, uint8_t *overflow) {
+    for (int i = 0; i < n; i++) {
+        int c = 0;
+        overflow[i] = 0;
+        for (int j = 0; j < i; j++) {
+            if (orc_dotf(v + (size_t)i * d, v + (size_t)j * d, d) >= threshold) {
+                if (c < ORC_MAX_FORM) near[(size_t)i * ORC_MAX_FORM + c] = j;
+                c++;
+            }
+        }
+        if (c > ORC_MAX_FORM) { overflow[i] = 1; c = 0; }
+        count[i] = c;
+    }
+}

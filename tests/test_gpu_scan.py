@@ -168,3 +168,28 @@ def test_resident_queries_match_search(lk):
     ids2, scores2, iscores2, counts2 = rq.fetch(0, 16, k)
     assert np.array_equal(ids, ids2) and np.array_equal(iscores, iscores2)
     assert np.array_equal(scores, scores2) and np.array_equal(counts, counts2)
+
+
+@pytest.mark.parametrize("n,dim,k", [(500, 64, 10), (20000, 768, 50), (3000, 100, 7), (9000, 1024, 20)])
+def test_f16_scan_matches_oracle(lk, n, dim, k):
+    """Half-precision storage (no counterpart in the reference: parity unpinned): rows are
+    normalised like the reference, rounded to IEEE half (nearest even), and scored against
+    the float32 query; the oracle accumulates the same values in float64."""
+    rows = gaussian_rows(n, dim, 500 + n)
+    queries = gaussian_rows(3, dim, 600 + n)
+    idx = lk.DeviceIndex(dim, lk.LK_F16)
+    idx.append(rows)
+    stored = idx.read_rows()
+    want_half = O.normalize_rows(rows).astype(np.float16)
+    assert np.array_equal(stored.view(np.uint16), want_half.view(np.uint16)), "stored halves differ"
+    deq = want_half.astype(np.float32)
+    ids, scores, _, counts = idx.search(queries, k)
+    kk = min(k, n)
+    for q in range(queries.shape[0]):
+        sc = O.scan_f32(deq, O.normalize(queries[q]))
+        wid, wsc = O.topk_f32(sc, k)
+        assert counts[q] == kk
+        np.testing.assert_allclose(scores[q, :kk], wsc, rtol=1e-5, atol=2e-7)
+        same = ids[q, :kk] == wid
+        for i in np.nonzero(~same)[0]:  # float32 accumulation: neighbours within rounding may swap
+            assert abs(sc[ids[q, i]] - wsc[i]) <= 1e-5 * max(abs(wsc[i]), 1e-6)
