@@ -65,17 +65,27 @@ __global__ void __launch_bounds__(kHamThreads) k_hamming_pairs(const unsigned lo
             rhi[r] = (unsigned)(v >> 32);
         }
         const int ncols = (int)min((long long)kHamTile, n - c0);
-#pragma unroll 4
-        for (int c = 0; c < ncols; ++c) {
-            const unsigned long long cv = cols[c];
-            const unsigned clo = (unsigned)cv, chi = (unsigned)(cv >> 32);
+        // Columns go by in chunks of 8.  The common case costs XOR + POPC + one compare that
+        // ORs into a per-chunk flag (no branch per pair); only a chunk with a low-word hit is
+        // looked at again, pair by pair, with the high words.
+        for (int cb = 0; cb < ncols; cb += 8) {
+            bool any = false;
 #pragma unroll
-            for (int r = 0; r < kHamRows; ++r) {
-                const int dlo = __popc(rlo[r] ^ clo);
-                if (dlo <= radius) {
-                    const int d = dlo + __popc(rhi[r] ^ chi);
-                    const long long cj = c0 + c;
-                    if (d <= radius && rid[r] < cj && rid[r] < n) ham_emit(out, count, cap, (unsigned)rid[r], (unsigned)cj);
+            for (int u = 0; u < 8; ++u) {
+                const unsigned clo = (unsigned)cols[cb + u];  // past ncols: zero padding, filtered below
+#pragma unroll
+                for (int r = 0; r < kHamRows; ++r) any |= __popc(rlo[r] ^ clo) <= radius;
+            }
+            if (any) {
+                for (int u = 0; u < 8 && cb + u < ncols; ++u) {
+                    const unsigned long long cv = cols[cb + u];
+                    const unsigned clo = (unsigned)cv, chi = (unsigned)(cv >> 32);
+                    const long long cj = c0 + cb + u;
+#pragma unroll
+                    for (int r = 0; r < kHamRows; ++r) {
+                        const int d = __popc(rlo[r] ^ clo) + __popc(rhi[r] ^ chi);
+                        if (d <= radius && rid[r] < cj && rid[r] < n) ham_emit(out, count, cap, (unsigned)rid[r], (unsigned)cj);
+                    }
                 }
             }
         }
