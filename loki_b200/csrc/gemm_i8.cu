@@ -42,15 +42,16 @@ constexpr int GM = 128;            // corpus rows per tile (MMA M, tensor-memory
 constexpr int GN = 128;            // queries per tile (MMA N, tensor-memory columns)
 constexpr int GSLICE = 128;        // K bytes per shared-memory slice: one swizzle row
 constexpr int GSLICE_BYTES = GM * GSLICE;  // 16 KB: one slice of a 128-row tile
-constexpr int GCAP_MAX = 512;      // most candidate keys a query holds between prunes (k <= 256)
+constexpr int GCAP_MAX = 1024;     // most candidate keys a query holds between prunes (k <= 256)
 constexpr int GEPI_WARPS = 8;      // epilogue warps: two per tensor-memory lane quadrant
 constexpr int GEPI_THREADS = GEPI_WARPS * 32;
 constexpr int GTHREADS = 64 + GEPI_THREADS;
-// A query's list holds cap = pow2ceil(k + 128) keys: one tile adds at most 128, so a list
-// is pruned back to k whenever it exceeds cap - 128.  Small lists keep the sorts short.
+// A query's list holds cap = pow2ceil(2k + 128) keys: one tile adds at most 128, so a list
+// is pruned back to k whenever it exceeds cap - 128, i.e. after at least k new survivors.
+// Small lists keep the sorts short; room for k newcomers keeps the prunes rare.
 __host__ __device__ inline int gemm_cap(int k) {
     int c = 256;
-    while (c < k + GM) c <<= 1;
+    while (c < 2 * k + GM) c <<= 1;
     return c;
 }
 constexpr long long GWAIT_CLOCKS = 4000000000ll;  // ~2 s at 2 GHz
