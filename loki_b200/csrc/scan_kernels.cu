@@ -93,29 +93,12 @@ struct TraitsF32 {
     }
     // float32 x float32 products are exact in float64, so fma here equals the
     // reference's multiply-then-add; only the order of the additions differs.
-#ifdef LK_F32_INTCVT
-    // float32 -> float64 widening with integer ops (exact for normal numbers and zero;
-    // denormals flush to zero, inf/nan are not handled): tuning experiment only
-    __device__ __forceinline__ static double widen(int b) {
-        const unsigned u = (unsigned)b;
-        unsigned hi = ((u >> 3) & 0x0fffffffu) + 0x38000000u;
-        hi = ((u & 0x7f800000u) == 0u) ? 0u : hi;
-        hi |= u & 0x80000000u;
-        const unsigned lo = ((u & 0x7f800000u) == 0u) ? 0u : (u << 29);
-        return __hiloint2double((int)hi, (int)lo);
-    }
-#else
     __device__ __forceinline__ static double widen(int b) { return (double)__int_as_float(b); }
-#endif
     __device__ __forceinline__ static void dot(acc_t &acc, const int4 &v, const QChunk &c) {
-#ifdef LK_EXP_NODOT
-        acc += __hiloint2double(v.x ^ v.y, v.z ^ v.w) + c.a.x;
-#else
         acc = fma(widen(v.x), c.a.x, acc);
         acc = fma(widen(v.y), c.a.y, acc);
         acc = fma(widen(v.z), c.b.x, acc);
         acc = fma(widen(v.w), c.b.y, acc);
-#endif
     }
     __device__ __forceinline__ static acc_t shfl(acc_t v, int m) {
         return __longlong_as_double((long long)shfl_xor_u64((uint64_t)__double_as_longlong(v), m));

@@ -88,3 +88,29 @@ def test_hamming_full_size_properties(lk):
     lo, hi = np.minimum(a, b), np.maximum(a, b)
     planted = lo.astype(np.uint64) << np.uint64(32) | hi.astype(np.uint64)
     assert np.isin(planted, packed).all()
+
+
+@pytest.mark.parametrize("radius", [0, 2, 3, 6, 9, 12, 20])
+def test_hamming_pairs_indexed_and_swept_paths(lk, radius):
+    """20,000 hashes: small radii take the multi-index path (buckets per bit field), large
+    radii the plain sweep; both must equal the oracle's all-pairs loop."""
+    h = phash_set(20000, 55, max_flips=12)
+    h[5] = h[19000]           # exact duplicates
+    h[6] = h[19000]
+    want, total = O.hamming_pairs(h, radius, cap=1 << 22)
+    got, cnt = lk.hamming_pairs(h, radius, cap=1 << 22)
+    assert cnt == total
+    assert np.array_equal(got, want)
+    parts = [lk.hamming_pairs(h, radius, part=p, parts=3, cap=1 << 22) for p in range(3)]
+    assert sum(c for _, c in parts) == total
+
+
+def test_hamming_pairs_skewed_buckets(lk):
+    """Many hashes sharing whole bit fields (one huge bucket in some tables) stay exact."""
+    rng = np.random.default_rng(3)
+    h = rng.integers(0, 2**64, size=12000, dtype=np.uint64)
+    h[:6000] &= np.uint64(0xFFFFFFFF00000000)       # low 32 bits all zero
+    h[3000:9000] |= np.uint64(0xFFFF000000000000)   # top 16 bits all one
+    want, total = O.hamming_pairs(h, 6, cap=1 << 22)
+    got, cnt = lk.hamming_pairs(h, 6, cap=1 << 22)
+    assert cnt == total and np.array_equal(got, want)
