@@ -19,30 +19,36 @@
 
 namespace lk {
 
-// One warp per row.  Shared memory per warp: dim floats (the row) + ld bytes (packed output).
+// One warp per row.  Shared memory per warp: dim doubles (squares) + dim floats (the row) + ld bytes (packed output).
 __global__ void __launch_bounds__(256) k_normalize_store(int type, const float *__restrict__ src, long long n,
                                                          int dim, unsigned char *__restrict__ dst, long long ld,
                                                          float *__restrict__ scales, int warps_per_cta) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (warp >= warps_per_cta) return;
-    const size_t per_warp = (size_t)round_up((long long)dim * 4, 16) + (size_t)ld;
-    float *x = reinterpret_cast<float *>(smem + per_warp * warp);
+    const size_t sq_bytes = (size_t)round_up((long long)dim * 8, 16);
+    const size_t per_warp = sq_bytes + (size_t)round_up((long long)dim * 4, 16) + (size_t)ld;
+    double *sq = reinterpret_cast<double *>(smem + per_warp * warp);
+    float *x = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(sq) + sq_bytes);
     unsigned char *packed = reinterpret_cast<unsigned char *>(x) + round_up((long long)dim * 4, 16);
 
     for (long long row = (long long)blockIdx.x * warps_per_cta + warp; row < n;
          row += (long long)gridDim.x * warps_per_cta) {
         const float *s = src + row * dim;
-        for (int i = lane; i < dim; i += 32) x[i] = s[i];
+        // All lanes widen their elements and square them (float32 squares are exact in
+        // float64); one lane then adds the squares in element order.  Splitting it this way
+        // keeps the conversions, which issue on a narrow pipe, off the one-lane chain.
+        for (int i = lane; i < dim; i += 32) {
+            const float f = s[i];
+            x[i] = f;
+            const double v = (double)f;
+            sq[i] = v * v;
+        }
         __syncwarp();
-        // sum of squares in element order, one lane, float64 (each square is exact)
         double norm = 0.0;
         if (lane == 0) {
             double sum = 0.0;
-            for (int i = 0; i < dim; ++i) {
-                const double v = (double)x[i];
-                sum = fma(v, v, sum);
-            }
+            for (int i = 0; i < dim; ++i) sum = __dadd_rn(sum, sq[i]);
             norm = (sum == 0.0) ? 0.0 : sqrt(sum);
         }
         norm = __shfl_sync(0xffffffffu, norm, 0);
@@ -143,7 +149,7 @@ __global__ void __launch_bounds__(256) k_centered_norm(const unsigned char *__re
 int normalize_store_launch(int type, const float *src, long long n, int dim, unsigned char *dst,
                            long long ld, float *scales, int sm_count, cudaStream_t stream) {
     if (n <= 0) return 0;
-    const size_t per_warp = (size_t)round_up((long long)dim * 4, 16) + (size_t)ld;
+    const size_t per_warp = (size_t)round_up((long long)dim * 8, 16) + (size_t)round_up((long long)dim * 4, 16) + (size_t)ld;
     int warps = (int)((96 * 1024) / per_warp);
     if (warps > 8) warps = 8;
     if (warps < 1) warps = 1;
