@@ -29,6 +29,7 @@
 
 #include <algorithm>
 
+#include "bulk.cuh"
 #include "scan.cuh"
 #include "topk.cuh"
 
@@ -486,35 +487,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const __grid_constant_
 #define LK_BULK_WARPS 4
 #endif
 constexpr int kBulkStages = LK_BULK_STAGES;
-constexpr unsigned kBulkSpinLimit = 1u << 22;  // bounded wait on a tile (each try blocks briefly in hardware)
-
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// global -> shared bulk copy; bytes and both addresses are multiples of 16
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, unsigned long long *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
 // SC > 0 fixes the slab width at compile time (SC 16-byte chunks, G must divide SC);
 // SC == 0 takes it from slab_bytes.  QREG keeps the query in registers (one slab per row).
 #ifdef LK_TIMELINE

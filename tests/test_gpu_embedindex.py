@@ -117,6 +117,45 @@ def test_shared_search_matches_oracle(impl, centered):
     _assert_hits_close(g, w, rel=2e-5)
 
 
+@pytest.mark.parametrize("npos,nneg", [(1, 0), (2, 0), (3, 1), (5, 2), (8, 0), (11, 3), (16, 0), (20, 2)])
+def test_shared_search_large_index_matches_oracle(lk, npos, nneg):
+    """Indexes of 8192 rows and more take the kernel that stages whole rows in shared
+    memory; every term-count class of it, with a ragged last batch of rows."""
+    n, dim, k = 9003, 200, 60
+    rows = np.stack([O.normalize(v) for v in _common_rows(n, dim, 51)])
+    idx = lk.DeviceIndex(dim, lk.LK_F32)
+    idx.append(rows)
+    stored = idx.read_rows(0, n)
+    pos = _common_rows(npos, dim, 52 + npos)
+    neg = _common_rows(nneg, dim, 53 + npos) if nneg else None
+    posw = list(np.linspace(0.5, 2.0, npos).astype(np.float32))
+    negw = list(np.linspace(0.25, 0.5, nneg).astype(np.float32)) if nneg else None
+    ids, scores = idx.search_shared(pos, posw=posw, neg=neg, negw=negw, k=k, scoring=lk.LK_SCORE_PLAIN)
+    sq = O.SharedQuery([O.normalize(p) for p in pos], posw, None if neg is None else [O.normalize(v) for v in neg], negw)
+    want = sq.scan(stored)
+    order = np.lexsort((np.arange(n), -want.astype(np.float64)))[:k]
+    assert len(ids) == k
+    np.testing.assert_allclose(scores, want[order], rtol=2e-5, atol=1e-6)
+    np.testing.assert_allclose(scores, want[ids], rtol=2e-5, atol=1e-6)   # each hit carries its own row's score
+    assert np.all(np.diff(scores) <= 0)
+
+
+def test_shared_search_large_centered_index_matches_oracle(impl):
+    n, dim, k = 8200, 64, 30
+    rows = _common_rows(n, dim, 61)
+    names = [f"c-{i:05d}" for i in range(n)]
+    gi, oi = impl.NewCentered(), OX.NewCentered()
+    gi.AddBatch(names, rows)
+    for p, v in zip(names, rows):
+        oi.Add(p, v)
+    pos = _common_rows(6, dim, 62)
+    neg = _common_rows(2, dim, 63)
+    for spec_kw in (dict(Pos=list(pos[:2])), dict(Pos=list(pos), Neg=list(neg), NegW=[0.5, 0.25])):
+        g = gi.SearchShared(impl.SharedSpec(**spec_kw), k, None)
+        w = oi.SearchShared(OX.SharedSpec(**spec_kw), k, None)
+        _assert_hits_close(g, w, rel=2e-5)
+
+
 def test_shared_errors_match_reference(impl):
     idx = impl.New()
     idx.Add("a", [1, 0])
