@@ -38,4 +38,9 @@ struct SharedArgs {
 int shared_scan_grid(int terms, int chunks, int k, int device, int *err);
 int shared_scan_launch(const SharedArgs &a, int terms, int grid, cudaStream_t stream);
 
+// The float64 tensor-core kernel for whole-row scans (shared_mma.cu).
+// shared_mma_launch: 0 = launched, 1 = not applicable (allow-list given, or nothing fits), else an error status.
+bool shared_mma_fits(int terms, long long ld, int k);
+int shared_mma_launch(const SharedArgs &a, int terms, int grid, cudaStream_t stream);
+
 }  // namespace lk

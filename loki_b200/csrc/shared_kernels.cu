@@ -9,12 +9,14 @@
 // norms) is O(terms^2 * dim) and stays on the host (hostmath.hpp).
 //
 // Shape: a skinny matrix product  rows[N x dim] * terms[dim x T], T <= 32, with
-// float64 accumulation like the reference.  A warp handles R rows at a time, lane l
-// reads 16-byte chunks l, l+32, ... of each row and keeps R x T partial sums; the
-// terms live in shared memory as float64.
+// float64 accumulation like the reference.  This file holds the gathering kernel, used
+// for allow-list scans (rows picked by slot) and for small indexes: a warp handles R
+// rows at a time, lane l reads 16-byte chunks l, l+32, ... of each row straight from
+// global memory and keeps R x T partial sums; the terms live in shared memory as float64.
+// Scans over all rows of a larger index run on the float64 tensor-core kernel in
+// shared_mma.cu, which this file's launcher tries first.
 #include <algorithm>
 
-#include "bulk.cuh"
 #include "lk_common.cuh"
 #include "shared.cuh"
 #include "topk.cuh"
@@ -244,265 +246,6 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_scan_shared(const SharedArg
     }
 }
 
-// ---------------------------------------------------------------------------
-// TMA-staged variant (whole rows, no allow-list): rows arrive in shared memory through
-// bulk asynchronous copies, RB rows (one contiguous copy) per stage, two stages per warp,
-// 8 warps per CTA, so that the bytes in flight do not depend on the registers the
-// RB x T float64 accumulators take.  The terms sit in shared memory as float32 and are
-// widened on the fly (shared by the RB rows of a batch).  The per-row scalar epilogue is
-// spread over the lanes: lane i of a row's lane group finishes positive i (serial over
-// the basis, in the reference's order); the weighted mean, spread and negatives are then
-// accumulated in index order from shuffled values, identically in every lane of the group.
-// ---------------------------------------------------------------------------
-constexpr int kShWarps = 8;
-constexpr int kShStages = 2;
-constexpr size_t kShSmemLimit = 220 * 1024;
-
-template <int TP, int RB>  // TP = power of two >= terms, RB rows per batch; RB * TP <= 32 and TP <= 32 / RB
-__global__ void __launch_bounds__(kShWarps * 32, 1) k_scan_shared_staged(const SharedArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int NV = RB * TP;
-    constexpr int LPR = 32 / RB;  // lanes per row in the epilogue
-    constexpr int T_THREADS = kShWarps * 32;
-    CandBuf buf;
-    buf.k = a.k;
-    buf.cap = cand_capacity(a.k);
-    buf.limit = buf.cap - kScanThreads;
-    buf.keys = reinterpret_cast<unsigned long long *>(smem);
-    buf.ctrl = reinterpret_cast<CandCtrl *>(smem + (size_t)buf.cap * 8);
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem + (size_t)buf.cap * 8 + 16);
-    double *dots_all = reinterpret_cast<double *>(bars + kShWarps * kShStages);   // [warps][NV]
-    float *terms = reinterpret_cast<float *>(dots_all + kShWarps * NV);           // [T][ld/4]
-    const SharedParams &P = *a.params;
-    const int T = P.m + P.rank + P.nneg;
-    const size_t stage_bytes = (size_t)RB * a.ld;
-    unsigned char *stages = smem + ((((size_t)((unsigned char *)(terms) - smem) + (size_t)T * a.ld) + 127) & ~(size_t)127);
-    __shared__ int s_last;
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) {
-        for (int i = 0; i < kShWarps * kShStages; ++i) mbar_init(&bars[i], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    const long long n_batches = (a.n + RB - 1) / RB;
-    const long long b_lo = n_batches * blockIdx.x / gridDim.x, b_hi = n_batches * (blockIdx.x + 1) / gridDim.x;
-    unsigned char *my_stages = stages + (size_t)warp * kShStages * stage_bytes;
-    unsigned long long *my_bars = bars + warp * kShStages;
-    double *dots = dots_all + warp * NV;
-    auto issue = [&](long long m) {  // batch m of this warp -> stage m % kShStages (lane 0 only)
-        const long long b = b_lo + warp + m * kShWarps;
-        if (b >= b_hi) return;
-        const long long row0 = b * RB;
-        const unsigned bytes = (unsigned)(min((long long)RB, a.n - row0) * a.ld);
-        const int s = (int)(m % kShStages);
-        mbar_expect_tx(&my_bars[s], bytes);
-        bulk_load(my_stages + (size_t)s * stage_bytes, a.rows + (size_t)row0 * a.ld, bytes, &my_bars[s]);
-    };
-    if (lane == 0)
-        for (int m = 0; m < kShStages; ++m) issue(m);
-
-    for (int i = tid; i < buf.cap; i += T_THREADS) buf.keys[i] = 0ull;
-    if (tid == 0) {
-        buf.ctrl->count = 0;
-        buf.ctrl->n_done = 0;
-        buf.ctrl->thr = 0ull;
-    }
-    for (int i = tid; i < T * (int)(a.ld / 16); i += T_THREADS)
-        reinterpret_cast<float4 *>(terms)[i] = reinterpret_cast<const float4 *>(a.terms)[i];
-    const unsigned long long bound = a.bound ? __ldcg(a.bound) : ~0ull;
-    __syncthreads();
-
-    long long m = 0;
-    bool counted = false, failed = false;
-    for (;;) {
-        const long long b = b_lo + warp + m * kShWarps;
-        const bool work = b < b_hi && !failed;
-        int seen = 0;
-        if (lane == 0) seen = *(volatile int *)&buf.ctrl->count;
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (work && seen <= buf.limit) {
-            const int s = (int)(m % kShStages);
-            unsigned spins = 0;
-            bool ready = false;
-            while (!(ready = mbar_try_wait(&my_bars[s], (unsigned)((m / kShStages) & 1))) && ++spins < kBulkSpinLimit) {}
-            if (!__all_sync(0xffffffffu, ready)) {
-                failed = true;  // the CTA still publishes what it has; the host sees the short count
-                continue;
-            }
-            const long long row0 = b * RB;
-            const int rows = (int)min((long long)RB, a.n - row0);
-            const unsigned char *stage = my_stages + (size_t)s * stage_bytes;
-            float inv[RB];
-            bool dead[RB];
-#pragma unroll
-            for (int r = 0; r < RB; ++r) {
-                inv[r] = 1.0f;
-                dead[r] = false;
-                if (a.cnorm != nullptr && r < rows) {
-                    const float cn = a.cnorm[row0 + r];
-                    dead[r] = cn < 1e-6f;
-                    inv[r] = dead[r] ? 0.0f : __fdiv_rn(1.0f, cn);
-                }
-            }
-            double acc[NV];
-#pragma unroll
-            for (int i = 0; i < NV; ++i) acc[i] = 0.0;
-            for (int j = lane; j < a.chunks; j += 32) {
-                double x[RB][4];
-                float4 m4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.cnorm != nullptr) m4 = reinterpret_cast<const float4 *>(a.mu)[j];
-#pragma unroll
-                for (int r = 0; r < RB; ++r) {
-                    float4 f = *reinterpret_cast<const float4 *>(stage + (size_t)r * a.ld + (size_t)j * 16);
-                    if (a.cnorm != nullptr) {  // (v - mu) * (1/cnorm), each step rounded to float32
-                        f.x = __fmul_rn(__fsub_rn(f.x, m4.x), inv[r]);
-                        f.y = __fmul_rn(__fsub_rn(f.y, m4.y), inv[r]);
-                        f.z = __fmul_rn(__fsub_rn(f.z, m4.z), inv[r]);
-                        f.w = __fmul_rn(__fsub_rn(f.w, m4.w), inv[r]);
-                    }
-                    x[r][0] = (double)f.x;
-                    x[r][1] = (double)f.y;
-                    x[r][2] = (double)f.z;
-                    x[r][3] = (double)f.w;
-                }
-#pragma unroll
-                for (int t = 0; t < TP; ++t) {
-                    if (t < T) {
-                        const float4 q = *reinterpret_cast<const float4 *>(terms + (size_t)t * (a.ld / 4) + (size_t)j * 4);
-                        const double q0 = (double)q.x, q1 = (double)q.y, q2 = (double)q.z, q3 = (double)q.w;
-#pragma unroll
-                        for (int r = 0; r < RB; ++r) {
-                            double sacc = acc[r * TP + t];
-                            sacc = fma(x[r][0], q0, sacc);
-                            sacc = fma(x[r][1], q1, sacc);
-                            sacc = fma(x[r][2], q2, sacc);
-                            sacc = fma(x[r][3], q3, sacc);
-                            acc[r * TP + t] = sacc;
-                        }
-                    }
-                }
-            }
-            __syncwarp();  // the stage is in registers: refill it
-            if (lane == 0) issue(m + kShStages);
-            ++m;
-            // reduce each accumulator over the warp; 32 at a time through the transposed butterfly
-#pragma unroll
-            for (int g0 = 0; g0 < NV; g0 += 32) {
-                constexpr int W = NV < 32 ? NV : 32;
-#pragma unroll
-                for (int w = 16; w >= W; w >>= 1)
-#pragma unroll
-                    for (int i = 0; i < W; ++i)
-                        acc[g0 + i] += __longlong_as_double((long long)shfl_xor_u64((uint64_t)__double_as_longlong(acc[g0 + i]), w));
-#pragma unroll
-                for (int w = W / 2; w >= 1; w >>= 1) {
-                    const bool upper = (lane & w) != 0;
-#pragma unroll
-                    for (int i = 0; i < w; ++i) {
-                        const double send = upper ? acc[g0 + i] : acc[g0 + i + w];
-                        const double keep = upper ? acc[g0 + i + w] : acc[g0 + i];
-                        acc[g0 + i] = keep + __longlong_as_double((long long)shfl_xor_u64((uint64_t)__double_as_longlong(send), w));
-                    }
-                }
-                if (lane < W) dots[g0 + lane] = acc[g0];  // lane i holds accumulator g0 + i
-            }
-            __syncwarp();
-            // ---- epilogue: media-server/embedvec/shared.go:186-218, lanes [r*LPR, (r+1)*LPR) own row r
-            const int r = lane / LPR, li = lane % LPR;
-            const double *d = dots + r * TP;  // float32-rounded like embedvec.Cosine when read below
-            double b2 = 0.0;
-            for (int j = 0; j < P.rank; ++j) {
-                const double vb = (double)(float)d[P.m + j];
-                b2 += vb * vb;  // exact product of two float32
-            }
-            double vn2 = __dsub_rn(1.0, __dmul_rn((double)P.gamma, b2));
-            if (vn2 < 1e-6) vn2 = 1e-6;
-            const double vn = sqrt(vn2);
-            double s_mine = 0.0;
-            if (li < P.m) {
-                double sv = (double)(float)d[li];
-                for (int j = 0; j < P.rank; ++j)
-                    sv = __dsub_rn(sv, __dmul_rn(__dmul_rn((double)P.gamma, (double)P.qb[li * P.rank + j]),
-                                                 (double)(float)d[P.m + j]));
-                s_mine = sv / __dmul_rn((double)P.posnorm[li], vn);
-            }
-            double mean = 0.0;
-            for (int i = 0; i < P.m; ++i) {
-                const double si = __longlong_as_double((long long)__shfl_sync(
-                    0xffffffffu, (unsigned long long)__double_as_longlong(s_mine), r * LPR + i));
-                mean = __dadd_rn(mean, __dmul_rn((double)P.posw[i], si));
-            }
-            double m2 = 0.0;
-            for (int i = 0; i < P.m; ++i) {
-                const double si = __longlong_as_double((long long)__shfl_sync(
-                    0xffffffffu, (unsigned long long)__double_as_longlong(s_mine), r * LPR + i));
-                const double dd = si - mean;
-                m2 = __dadd_rn(m2, __dmul_rn(__dmul_rn((double)P.posw[i], dd), dd));
-            }
-            double o = __dsub_rn(mean, __dmul_rn((double)P.lambda, sqrt(m2)));
-            for (int i = 0; i < P.nneg; ++i)
-                o = __dsub_rn(o, __dmul_rn((double)P.negw[i], (double)(float)d[P.m + P.rank + i]));
-            bool pass = false;
-            unsigned long long key = 0ull;
-            if (li == 0 && r < rows) {
-                bool dr = false;
-#pragma unroll
-                for (int rr = 0; rr < RB; ++rr)
-                    if (rr == r) dr = dead[rr];
-                const float out = dr ? 0.0f : (float)o;
-                key = make_key(ord_from_f32(out), (unsigned)(row0 + r));
-                const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
-                pass = key > thr && key < bound;
-            }
-            cand_offer_warp(buf, pass, key);
-            continue;
-        }
-        if (!work && !counted) {
-            if (lane == 0) atomicAdd(&buf.ctrl->n_done, 1);
-            counted = true;
-        }
-        __syncthreads();
-        const int c = buf.ctrl->count, nd = buf.ctrl->n_done;
-        __syncthreads();
-        if (c > buf.limit || nd == kShWarps) cand_prune(buf);
-        if (nd == kShWarps) break;
-    }
-    __shared__ int s_failed;
-    if (tid == 0) s_failed = 0;
-    __syncthreads();
-    if (failed && lane == 0) s_failed = 1;
-    __syncthreads();
-
-    unsigned long long *mine = a.part + (size_t)blockIdx.x * a.k;
-    for (int i = tid; i < a.k; i += T_THREADS) mine[i] = buf.keys[i];
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        if (s_failed) atomicExch(reinterpret_cast<int *>(a.ticket + 1), 1);
-        s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    cand_select_from_lists(buf, a.part, (int)gridDim.x);
-    const int cnt = buf.ctrl->count;
-    for (int i = tid; i < a.k; i += T_THREADS) {
-        const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
-        a.out_keys[i] = key;
-        a.out_ids[i] = key ? a.shard_base + (long long)key_slot(key) : -1;
-        a.out_scores[i] = key ? f32_from_ord(key_ord(key)) : 0.0f;
-        if (a.out_iscores) a.out_iscores[i] = 0;
-    }
-    if (tid == 0) {
-        int *err = reinterpret_cast<int *>(a.ticket + 1);
-        const bool bad = *(volatile int *)err != 0;
-        *a.out_count = bad ? -1 : cnt;
-        *err = 0;
-        *a.ticket = 0u;
-    }
-}
-
 typedef void (*shared_fn)(const SharedArgs);
 
 static shared_fn pick_shared(int terms) {
@@ -518,20 +261,7 @@ static size_t shared_smem(int terms, int chunks, int k) {
     return (size_t)cand_capacity(k) * 8 + 16 + (size_t)terms * chunks * 32;
 }
 
-static shared_fn pick_staged(int terms) {
-    if (terms <= 2) return k_scan_shared_staged<2, 4>;
-    if (terms <= 4) return k_scan_shared_staged<4, 4>;
-    if (terms <= 8) return k_scan_shared_staged<8, 4>;
-    if (terms <= 16) return k_scan_shared_staged<16, 2>;
-    return k_scan_shared_staged<32, 1>;
-}
-static int staged_rows(int terms) { return terms <= 8 ? 4 : (terms <= 16 ? 2 : 1); }
-static int staged_tp(int terms) { return terms <= 2 ? 2 : (terms <= 4 ? 4 : (terms <= 8 ? 8 : (terms <= 16 ? 16 : 32))); }
-static size_t staged_smem(int terms, long long ld, int k) {
-    const size_t head = (size_t)cand_capacity(k) * 8 + 16 + kShWarps * kShStages * 8 +
-                        (size_t)kShWarps * staged_rows(terms) * staged_tp(terms) * 8 + (size_t)terms * ld;
-    return ((head + 127) & ~(size_t)127) + (size_t)kShWarps * kShStages * staged_rows(terms) * ld;
-}
+constexpr size_t kShSmemLimit = 220 * 1024;
 
 int shared_scan_grid(int terms, int chunks, int k, int device, int *err) {
     *err = 0;
@@ -540,8 +270,9 @@ int shared_scan_grid(int terms, int chunks, int k, int device, int *err) {
     if (e != cudaSuccess) { *err = (int)e; return 0; }
     const size_t smem = shared_smem(terms, chunks, k);
     if (smem > kShSmemLimit) {
-        // only the staged kernel (float32 terms) can hold them: it runs one CTA per SM
-        if (staged_smem(terms, (long long)chunks * 16, k) > kShSmemLimit) { *err = -1; return 0; }
+        // too many terms to keep widened beside the candidates: only the tensor-core kernel
+        // (float32 terms, one CTA per SM) can take them
+        if (!shared_mma_fits(terms, (long long)chunks * 16, k)) { *err = -1; return 0; }
         return sms;
     }
     shared_fn fn = pick_shared(terms);
@@ -555,23 +286,13 @@ int shared_scan_grid(int terms, int chunks, int k, int device, int *err) {
 }
 
 int shared_scan_launch(const SharedArgs &a, int terms, int grid, cudaStream_t stream) {
-    // whole contiguous rows and enough of them: the TMA-staged kernel, one CTA per SM
-    const size_t st_smem = staged_smem(terms, a.ld, a.k);
     const bool old_fits = shared_smem(terms, a.chunks, a.k) <= kShSmemLimit;
-    if (a.slots != nullptr && !old_fits) return fail(7, "shared scan: terms x dim too large for an allow-list scan");
-    if (a.slots == nullptr && st_smem <= kShSmemLimit && (a.n >= 8192 || !old_fits)) {
-        shared_fn fn = pick_staged(terms);
-        cudaError_t e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem);
-        if (e != cudaSuccess) return fail(4, std::string("shared scan attr: ") + cudaGetErrorString(e));
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int g = std::min(sms, grid);  // the caller sized its per-CTA scratch for `grid` CTAs
-        fn<<<g, kShWarps * 32, st_smem, stream>>>(a);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return fail(4, std::string("shared scan launch: ") + cudaGetErrorString(e));
-        return 0;
+    // whole contiguous rows and enough of them: the float64 tensor-core kernel, one CTA per SM
+    if (a.slots == nullptr && (a.n >= 8192 || !old_fits)) {
+        const int st = shared_mma_launch(a, terms, grid, stream);
+        if (st != 1) return st;
     }
+    if (!old_fits) return fail(7, "shared scan: terms x dim too large for this scan");
     shared_fn fn = pick_shared(terms);
     const size_t smem = shared_smem(terms, a.chunks, a.k);
     if (a.n < grid) grid = (int)(a.n > 0 ? a.n : 1);

@@ -117,11 +117,20 @@ def test_shared_search_matches_oracle(impl, centered):
     _assert_hits_close(g, w, rel=2e-5)
 
 
-@pytest.mark.parametrize("npos,nneg", [(1, 0), (2, 0), (3, 1), (5, 2), (8, 0), (11, 3), (16, 0), (20, 2)])
+@pytest.mark.parametrize("npos,nneg", [(1, 0), (2, 0), (3, 1), (5, 2), (8, 0), (11, 3), (16, 1), (4, 0)])
 def test_shared_search_large_index_matches_oracle(lk, npos, nneg):
     """Indexes of 8192 rows and more take the kernel that stages whole rows in shared
     memory; every term-count class of it, with a ragged last batch of rows."""
-    n, dim, k = 9003, 200, 60
+    _shared_large_case(lk, 9003, 200, 60, npos, nneg)
+
+
+def test_shared_search_large_index_many_terms_wide_rows(lk):
+    """31 query-side vectors of 768 floats do not fit in shared memory as float64: the
+    kernel keeps them as float32 and widens them per batch of rows."""
+    _shared_large_case(lk, 8210, 768, 25, 16, 0)
+
+
+def _shared_large_case(lk, n, dim, k, npos, nneg):
     rows = np.stack([O.normalize(v) for v in _common_rows(n, dim, 51)])
     idx = lk.DeviceIndex(dim, lk.LK_F32)
     idx.append(rows)
