@@ -9,17 +9,20 @@
 // int32 dots of the single-query scan, and ranking uses the same 64-bit keys, so the
 // result is bit-identical to running the queries one by one.
 //
-// Shape of one CTA (320 threads, one CTA per SM):
+// Shape of one CTA (576 threads, one CTA per SM):
 //   warp 0     TMA producer: 2-D tiled loads (128-byte swizzle) of corpus tiles
 //              [128 rows x 128 K-bytes] into a ring of stages; loads the CTA's query
 //              tile [128 queries x all K] once, it stays resident in shared memory
 //   warp 1     allocates tensor memory and issues the MMAs: D[128 rows x 128 queries]
 //              += A[128 x 32] * B[128 x 32]^T, four per 128-byte K slice; commits free
 //              the stage / publish the accumulator through mbarriers
-//   warps 2-9  epilogue: read the accumulator from tensor memory (one corpus row and 64
-//              queries per thread), compare with each query's running threshold and
-//              append the few survivors to that query's candidate list; two accumulator
-//              buffers let the next tile's MMAs run meanwhile
+//   warps 2-17 epilogue: read the accumulator from tensor memory (one corpus row and 32
+//              queries per thread), test all 32 scores against the queries' running
+//              thresholds with one add and half an OR each, and append the few survivors to
+//              their queries' candidate lists; four accumulator buffers (all of tensor memory)
+//              let the following tiles' MMAs run meanwhile.  A list that fills up is cut back to its best k by a
+//              warp-wide selection (bisection on the score with the keys in registers), which
+//              also raises the query's threshold; lists are sorted once, at the end.
 // A CTA owns one tile of 128 queries and every ns-th corpus tile; the CTAs of one query
 // tile split the corpus between them and their lists are merged by k_merge_lists.
 //
@@ -43,15 +46,17 @@ constexpr int GN = 128;            // queries per tile (MMA N, tensor-memory col
 constexpr int GSLICE = 128;        // K bytes per shared-memory slice: one swizzle row
 constexpr int GSLICE_BYTES = GM * GSLICE;  // 16 KB: one slice of a 128-row tile
 constexpr int GCAP_MAX = 1024;     // most candidate keys a query holds between prunes (k <= 256)
-constexpr int GEPI_WARPS = 8;      // epilogue warps: two per tensor-memory lane quadrant
+constexpr int GEPI_WARPS = 16;     // epilogue warps: four per tensor-memory lane quadrant, 32 queries each
 constexpr int GEPI_THREADS = GEPI_WARPS * 32;
 constexpr int GTHREADS = 64 + GEPI_THREADS;
-// A query's list holds cap = pow2ceil(2k + 128) keys: one tile adds at most 128, so a list
-// is pruned back to k whenever it exceeds cap - 128, i.e. after at least k new survivors.
-// Small lists keep the sorts short; room for k newcomers keeps the prunes rare.
+constexpr int GACC = 4;            // accumulators in tensor memory: 4 x 128 columns = all 512
+// A query's list holds cap = pow2ceil(2k + 256) keys.  One tile adds at most 128; the check
+// that triggers a prune may miss what other warps append while it runs, so it leaves room
+// for two tiles: a list is cut back to k whenever it exceeds cap - 256, i.e. after at least
+// k new survivors.  Small lists keep the selections short and the thresholds fresh.
 __host__ __device__ inline int gemm_cap(int k) {
-    int c = 256;
-    while (c < 2 * k + GM) c <<= 1;
+    int c = 512;
+    while (c < 2 * k + 2 * GM) c <<= 1;
     return c;
 }
 constexpr long long GWAIT_CLOCKS = 4000000000ll;  // ~2 s at 2 GHz
@@ -70,6 +75,17 @@ __device__ __forceinline__ void g_mbar_arrive(unsigned long long *bar) {
 // Bounded wait for the phase with the given parity; false when the clock ran out or
 // another role of this CTA has already given up.
 __device__ __forceinline__ bool g_mbar_wait(unsigned long long *bar, unsigned parity, volatile int *cta_failed) {
+    {   // usually the phase is already complete: no clock read on that path
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(g_smem(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
     const long long t0 = clock64();
     for (;;) {
         unsigned ok;
@@ -160,17 +176,16 @@ __device__ unsigned long long g_gemm_prof[16];  // summed clocks per role and ph
 #endif
 
 struct GemmShared {  // control words behind the data regions
-    unsigned long long full[8], empty[8], b_full, tmem_full[2], tmem_empty[2];
+    unsigned long long full[8], empty[8], b_full, tmem_full[GACC], tmem_empty[GACC];
     unsigned long long thr[GN];  // per query: keys must exceed this to enter its list
     alignas(16) int thr_score[GN];  // score part of thr: the cheap first test (score >= thr_score)
     int cnt[GN];                 // per query: keys in its list
     unsigned tmem_base;
-    int need_prune;
     int failed;           // any role gave up waiting
     int epilogue_failed;  // written by epilogue threads only (their common exit decision)
 };
 
-// Sort n (<= cap) keys of one query in this warp's scratch, descending; n padded to a power of two.
+// Sort sz (a power of two) keys in this warp's scratch, descending.
 __device__ inline void g_warp_sort_desc(unsigned long long *s, int sz, int lane) {
     for (int size = 2; size <= sz; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -188,38 +203,101 @@ __device__ inline void g_warp_sort_desc(unsigned long long *s, int sz, int lane)
     }
 }
 
-// Keep the best k keys of query q's list (global memory) and raise its threshold.
-__device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q, unsigned long long *scratch, int q,
-                                     int k, int cap, int lane) {
-    const int n = min(ctl->cnt[q], cap);
-    int sz = 2;
-    while (sz < n) sz <<= 1;
-    {
-        unsigned long long r[GCAP_MAX / 32];  // all loads in flight at once
+// Cut query q's list (global memory, unordered) back to its best k keys and raise the query's
+// threshold to the k-th.  No sort: the k-th largest key is found by bisection on the score
+// word with warp-wide counts (the keys sit in registers, KPL per lane), ties on that score
+// are settled by a second bisection on the slot word, and the keepers are compacted in place.
+template <int KPL>
+__device__ inline void g_select_query(GemmShared *ctl, unsigned long long *cand_q, int q, int k, int lane) {
+    const int n = min(ctl->cnt[q], KPL * 32);
+    if (n <= k) return;
+    unsigned hi[KPL], lo[KPL];  // score word (0 = no key: below every real one) and slot word
 #pragma unroll
-        for (int u = 0; u < GCAP_MAX / 32; ++u) {
-            const int i = lane + 32 * u;
-            r[u] = (i < n) ? __ldcg(cand_q + i) : 0ull;
-        }
-#pragma unroll
-        for (int u = 0; u < GCAP_MAX / 32; ++u) {
-            const int i = lane + 32 * u;
-            if (i < sz) scratch[i] = r[u];
-        }
+    for (int u = 0; u < KPL; ++u) {
+        const int i = lane + 32 * u;
+        const unsigned long long key = (i < n) ? __ldcg(cand_q + i) : 0ull;
+        hi[u] = (unsigned)(key >> 32);
+        lo[u] = (unsigned)key;
     }
+    unsigned mx = 0, mn = 0xffffffffu;
+#pragma unroll
+    for (int u = 0; u < KPL; ++u) {
+        mx = max(mx, hi[u]);
+        if (hi[u] != 0u) mn = min(mn, hi[u]);
+    }
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    mn = __reduce_min_sync(0xffffffffu, mn);
+    // X = the largest score word x with count(hi >= x) >= k;  count(hi >= mn) = n > k
+    unsigned a = mn, b = mx + 1u;  // count(hi >= a) >= k, count(hi >= b) < k
+    while (b - a > 1u) {
+        const unsigned mid = a + ((b - a) >> 1);
+        int c = 0;
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) c += (hi[u] >= mid) ? 1 : 0;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (c >= k) a = mid; else b = mid;
+    }
+    const unsigned X = a;
+    int c_gt = 0, c_eq = 0;
+#pragma unroll
+    for (int u = 0; u < KPL; ++u) {
+        c_gt += (hi[u] > X) ? 1 : 0;
+        c_eq += (hi[u] == X) ? 1 : 0;
+    }
+    c_gt = __reduce_add_sync(0xffffffffu, c_gt);
+    c_eq = __reduce_add_sync(0xffffffffu, c_eq);
+    const int need = k - c_gt;  // 1 <= need <= c_eq keys of score X stay: those with the largest slot words
+    unsigned Y = 0u;
+    if (need < c_eq) {  // rare: more equal scores than places
+        unsigned long long ya = 0ull, yb = 0x100000000ull;  // count(tie && lo >= ya) >= need > count(tie && lo >= yb)
+        while (yb - ya > 1ull) {
+            const unsigned long long mid = ya + ((yb - ya) >> 1);
+            int c = 0;
+#pragma unroll
+            for (int u = 0; u < KPL; ++u) c += (hi[u] == X && lo[u] >= mid) ? 1 : 0;
+            c = __reduce_add_sync(0xffffffffu, c);
+            if (c >= need) ya = mid; else yb = mid;
+        }
+        Y = (unsigned)ya;
+    }
+    // compaction: lane-local count, exclusive scan over lanes, stores behind all loads
+    int mine = 0;
+    unsigned ymin = 0xffffffffu;
+#pragma unroll
+    for (int u = 0; u < KPL; ++u) {
+        const bool keep = hi[u] > X || (hi[u] == X && lo[u] >= Y);
+        mine += keep ? 1 : 0;
+        if (hi[u] == X && lo[u] >= Y) ymin = min(ymin, lo[u]);
+    }
+    int pos = mine;
+#pragma unroll
+    for (int w = 1; w < 32; w <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, pos, w);
+        if (lane >= w) pos += o;
+    }
+    pos -= mine;
+    ymin = __reduce_min_sync(0xffffffffu, ymin);
     __syncwarp();
-    g_warp_sort_desc(scratch, sz, lane);
-    const int keep = min(n, k);
-    for (int i = lane; i < keep; i += 32) __stcg(cand_q + i, scratch[i]);
+#pragma unroll
+    for (int u = 0; u < KPL; ++u) {
+        const bool keep = hi[u] > X || (hi[u] == X && lo[u] >= Y);
+        if (keep) __stcg(cand_q + pos++, ((unsigned long long)hi[u] << 32) | lo[u]);
+    }
     __syncwarp();
     if (lane == 0) {
-        ctl->cnt[q] = keep;
-        if (keep == k && scratch[k - 1] > ctl->thr[q]) {
-            ctl->thr[q] = scratch[k - 1];
-            ctl->thr_score[q] = i32_from_ord(key_ord(scratch[k - 1]));
+        ctl->cnt[q] = k;
+        const unsigned long long kth = ((unsigned long long)X << 32) | ymin;  // the smallest key kept
+        if (kth > ctl->thr[q]) {
+            ctl->thr[q] = kth;
+            ctl->thr_score[q] = i32_from_ord(X);
         }
     }
     __syncwarp();
+}
+
+__device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q, int q, int k, int cap, int lane) {
+    if (cap <= 512) g_select_query<16>(ctl, cand_q, q, k, lane);
+    else g_select_query<GCAP_MAX / 32>(ctl, cand_q, q, k, lane);
 }
 
 __global__ void __launch_bounds__(GTHREADS, 1)
@@ -230,9 +308,8 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     unsigned char *smem = g_raw + ((1024u - (g_smem(g_raw) & 1023u)) & 1023u);
     unsigned char *sm_b = smem;                                        // [ks][128 queries][128 B]
     unsigned char *sm_a = sm_b + (size_t)a.ks * GSLICE_BYTES;          // [stages][128 rows][128 B]
-    unsigned long long *sm_scratch = reinterpret_cast<unsigned long long *>(sm_a + (size_t)a.stages * GSLICE_BYTES);
-    const int cap = gemm_cap(a.k), limit = cap - GM;
-    GemmShared *ctl = reinterpret_cast<GemmShared *>(sm_scratch + (size_t)GEPI_WARPS * cap);
+    const int cap = gemm_cap(a.k), limit = cap - 2 * GM;
+    GemmShared *ctl = reinterpret_cast<GemmShared *>(sm_a + (size_t)a.stages * GSLICE_BYTES);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int qt, slice, nslices;
@@ -247,11 +324,10 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
             g_mbar_init(&ctl->empty[i], 1);
         }
         g_mbar_init(&ctl->b_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < GACC; ++i) {
             g_mbar_init(&ctl->tmem_full[i], 1);
             g_mbar_init(&ctl->tmem_empty[i], GEPI_WARPS);  // one arrival per epilogue warp
         }
-        ctl->need_prune = 0;
         ctl->failed = 0;
         ctl->epilogue_failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -259,13 +335,13 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     if (tid < GN) {
         const bool live = q0 + tid < a.nq;  // queries past the end accept nothing
         ctl->thr[tid] = live ? 0ull : ~0ull;
-        ctl->thr_score[tid] = live ? (int)0x80000000 : 0x7fffffff;
+        ctl->thr_score[tid] = live ? -(1 << 30) : (1 << 30);  // every real score is far inside +-2^30
         ctl->cnt[tid] = 0;
     }
-    if (warp == 1) {  // tensor memory: 2 accumulators x 128 columns
+    if (warp == 1) {  // tensor memory: GACC accumulators x 128 columns
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(g_smem(&ctl->tmem_base)),
-                     "r"(2 * GN)
+                     "r"(GACC * GN)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -300,6 +376,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             bool ok = g_mbar_wait(&ctl->b_full, 0u, failed);
+            const unsigned long long da0 = g_smem_desc(g_smem(sm_a)), db0 = g_smem_desc(g_smem(sm_b));
             int stage = 0, acc = 0;
             unsigned phase = 0, acc_phase = 0;
             for (long long t = slice; ok && t < n_tiles; t += nslices) {
@@ -311,8 +388,9 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
                     { GPROF_T0; ok = g_mbar_wait(&ctl->full[stage], phase, failed); GPROF_ADD(2); }
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned long long da = g_smem_desc(g_smem(sm_a + (size_t)stage * GSLICE_BYTES));
-                    const unsigned long long db = g_smem_desc(g_smem(sm_b + (size_t)s * GSLICE_BYTES));
+                    // the start-address field counts 16-byte units: one slice further = + 1024
+                    const unsigned long long da = da0 + (unsigned long long)(stage * (GSLICE_BYTES >> 4));
+                    const unsigned long long db = db0 + (unsigned long long)(s * (GSLICE_BYTES >> 4));
 #pragma unroll
                     for (int k4 = 0; k4 < GSLICE / 32; ++k4)  // 32 K-bytes per MMA: +2 in 16-byte units
                         g_mma_i8(d, da + (unsigned long long)(2 * k4), db + (unsigned long long)(2 * k4), (s | k4) != 0);
@@ -324,7 +402,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
                 }
                 if (!ok) break;
                 g_mma_commit(&ctl->tmem_full[acc]);  // accumulator complete
-                if (++acc == 2) {
+                if (++acc == GACC) {
                     acc = 0;
                     acc_phase ^= 1u;
                 }
@@ -332,29 +410,25 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        // 8 warps: warp w reads tensor-memory lanes 32*(w%4).. (the hardware's rule) and the
-        // column half (w-2)/4, i.e. one corpus row x 64 queries per thread and tile.
-        const int ew = warp - 2;       // 0..7
+        // 16 warps: a warp may read the tensor-memory lanes 32 * (warp % 4) .. + 31 (the hardware's
+        // rule), i.e. 32 corpus rows, and takes one quarter of the 128 query columns: one corpus
+        // row x 32 queries per thread and tile.
+        const int ew = warp - 2;       // 0..15
         const int quad = warp & 3;
-        const int half = ew >> 2;
+        const int c0 = (ew >> 2) * 32;
         const int etid = ew * 32 + lane;
         unsigned long long *cand = a.cand + (size_t)blockIdx.x * GN * GCAP_MAX;
-        unsigned long long *scratch = sm_scratch + (size_t)ew * cap;
         int acc = 0;
         unsigned acc_phase = 0;
         bool ok = true;
         for (long long t = slice; t < n_tiles; t += nslices) {
-            // all epilogue threads must take the same exit: vote through a word only they write
-            { GPROF_T0; if (!g_mbar_wait(&ctl->tmem_full[acc], acc_phase, failed)) ctl->epilogue_failed = 1; if (etid == 0) GPROF_ADD(3); }
+            bool have;
+            { GPROF_T0; have = g_mbar_wait(&ctl->tmem_full[acc], acc_phase, failed); if (etid == 0) GPROF_ADD(3); }
             GPROF_T0;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            ok = ctl->epilogue_failed == 0;
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const long long row = t * GM + quad * 32 + lane;
-            const bool valid = row < a.n;
-#pragma unroll 1
-            for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+            if (!have) ctl->epilogue_failed = 1;  // read by all epilogue threads behind the barrier below
+            if (have) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const long long row = t * GM + quad * 32 + lane;
                 int v[32];
                 g_tmem_ld32(tmem_base + (unsigned)(acc * GN + c0) + ((unsigned)(quad * 32) << 16), v);
                 // the 32 score thresholds of these queries, while the load is in flight
@@ -365,61 +439,89 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
                     ts[j] = w.x; ts[j + 1] = w.y; ts[j + 2] = w.z; ts[j + 3] = w.w;
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                unsigned pass = 0;  // branch-free first test: one bit per query of the chunk
+                // first test, branch-free: ts - v - 1 is negative exactly when v >= ts (both are far
+                // from the ends of the int range), so the sign of the OR says "some query accepts"
+                int any = 0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) pass |= (v[j] >= ts[j] ? 1u : 0u) << j;
-                if (!valid) pass = 0;
-                while (pass) {  // rare once the thresholds have risen
-                    const int j = __ffs(pass) - 1;
-                    pass &= pass - 1;
-                    int sv = 0;
+                for (int j = 0; j < 32; ++j) any |= ts[j] - v[j] - 1;
+                const bool mine = any < 0 && row < a.n;
+                if (__any_sync(0xffffffffu, mine)) {  // some lane has a survivor: rare once the thresholds have risen
+                    // column by column, the whole warp: the lanes that pass column j all append to
+                    // the same query, so one atomic reserves their places
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj)
-                        if (jj == j) sv = v[jj];
-                    const int q = c0 + j;
-                    const unsigned long long key = make_key(ord_from_i32(sv), (unsigned)row);
-                    if (key > ctl->thr[q]) {
-                        const int pos = atomicAdd(&ctl->cnt[q], 1);
-                        if (pos < cap) __stcg(cand + (size_t)q * GCAP_MAX + pos, key);
+                    for (int j = 0; j < 32; ++j) {
+                        const bool p = mine && v[j] >= ts[j];
+                        const unsigned m = __ballot_sync(0xffffffffu, p);
+                        if (m != 0u) {
+                            const int q = c0 + j;
+                            const unsigned long long key = make_key(ord_from_i32(v[j]), (unsigned)row);
+                            const unsigned m2 = __ballot_sync(0xffffffffu, p && key > ctl->thr[q]);
+                            if (m2 != 0u) {
+                                int base = 0;
+                                if (lane == __ffs(m2) - 1) base = atomicAdd(&ctl->cnt[q], __popc(m2));
+                                base = __shfl_sync(0xffffffffu, base, __ffs(m2) - 1);
+                                const int pos = base + __popc(m2 & lanemask_lt());
+                                if (((m2 >> lane) & 1u) && pos < cap) __stcg(cand + (size_t)q * GCAP_MAX + pos, key);
+                            }
+                        }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) g_mbar_arrive(&ctl->tmem_empty[acc]);
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) g_mbar_arrive(&ctl->tmem_empty[acc]);
             if (etid == 0) GPROF_ADD(4);
-            if (++acc == 2) {
+            if (++acc == GACC) {
                 acc = 0;
                 acc_phase ^= 1u;
             }
-            // lists that could overflow on the next tile are pruned now (all warps take part)
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (etid < GN && ctl->cnt[etid] > limit) ctl->need_prune = 1;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (ctl->need_prune) {
+            // One barrier per tile: it also ORs "one of my lists passed the mark".  The count a
+            // thread reads may miss appends of warps still working on this tile; the mark
+            // leaves room for that (see gemm_cap) and the next tile's check sees them.
+            const int over = (etid < GN && ctl->cnt[etid] > limit) ? 1 : 0;
+            int prune;
+            asm volatile(
+                "{\n\t.reg .pred p, r;\n\t"
+                "setp.ne.s32 p, %1, 0;\n\t"
+                "bar.red.or.pred r, 1, 512, p;\n\t"
+                "selp.s32 %0, 1, 0, r;\n\t}"
+                : "=r"(prune)
+                : "r"(over)
+                : "memory");
+            ok = ctl->epilogue_failed == 0;
+            if (!ok) break;
+            if (prune) {
                 GPROF_T0;
                 __threadfence();
-                // every list above k is pruned, not only the full ones: the queries of a tile fill at
+                // every list above k is cut, not only the full ones: the queries of a tile fill at
                 // similar rates, so this turns hundreds of one-list stalls into a handful of events
-                // in which all eight warps sort at once
+                // in which all warps work at once
                 for (int q = ew; q < GN; q += GEPI_WARPS)
-                    if (ctl->cnt[q] > a.k) g_prune_query(ctl, cand + (size_t)q * GCAP_MAX, scratch, q, a.k, cap, lane);
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (etid == 0) ctl->need_prune = 0;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (ctl->cnt[q] > a.k) g_prune_query(ctl, cand + (size_t)q * GCAP_MAX, q, a.k, cap, lane);
+                asm volatile("bar.sync 1, 512;" ::: "memory");
                 if (etid == 0) GPROF_ADD(5);
             }
         }
-        // final lists of this CTA: [slice][query][k]
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        // final lists of this CTA: [slice][query][k], ranked.  The corpus stages are idle by now
+        // (the last accumulator was complete before the last tile was read): they are the sort scratch.
+        asm volatile("bar.sync 1, 512;" ::: "memory");
         __threadfence();
-        for (int q = ew; q < GN; q += GEPI_WARPS) {
-            if (q0 + q >= a.nq) continue;
-            g_prune_query(ctl, cand + (size_t)q * GCAP_MAX, scratch, q, a.k, cap, lane);
-            const int keep = ok ? ctl->cnt[q] : 0;
-            unsigned long long *dst = a.lists + ((size_t)slice * a.nq + (q0 + q)) * a.k;
-            for (int i = lane; i < a.k; i += 32) dst[i] = (i < keep) ? scratch[i] : 0ull;
-            __syncwarp();
+        int ksz = 2;
+        while (ksz < a.k) ksz <<= 1;
+        const int sorters = min(GEPI_WARPS, (int)((size_t)a.stages * GSLICE_BYTES / ((size_t)ksz * 8)));
+        if (ew < sorters) {
+            unsigned long long *scratch = reinterpret_cast<unsigned long long *>(sm_a) + (size_t)ew * ksz;
+            for (int q = ew; q < GN; q += sorters) {
+                if (q0 + q >= a.nq) continue;
+                g_prune_query(ctl, cand + (size_t)q * GCAP_MAX, q, a.k, cap, lane);
+                const int keep = ok ? min(ctl->cnt[q], a.k) : 0;
+                for (int i = lane; i < ksz; i += 32) scratch[i] = (i < keep) ? __ldcg(cand + (size_t)q * GCAP_MAX + i) : 0ull;
+                __syncwarp();
+                g_warp_sort_desc(scratch, ksz, lane);
+                unsigned long long *dst = a.lists + ((size_t)slice * a.nq + (q0 + q)) * a.k;
+                for (int i = lane; i < a.k; i += 32) dst[i] = scratch[i];
+                __syncwarp();
+            }
         }
     }
     // ------------------------------ teardown ------------------------------
@@ -428,7 +530,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     if (tid == 0 && ctl->failed != 0 && a.error != nullptr) atomicExch(a.error, 1);
     if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * GN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GACC * GN) : "memory");
     }
 }
 
@@ -500,9 +602,9 @@ int gemm_launch(const unsigned char *d_rows, long long n, long long ld, const un
     LK_TRY(make_map(&tm_rows, d_rows, n, ld));
     LK_TRY(make_map(&tm_q, d_queries, nq, ld));
     const int ks = (int)((ld + GSLICE - 1) / GSLICE);
-    const size_t fixed = (size_t)ks * GSLICE_BYTES + (size_t)GEPI_WARPS * gemm_cap(k) * 8 + sizeof(GemmShared) + 1024;
+    const size_t fixed = (size_t)ks * GSLICE_BYTES + sizeof(GemmShared) + 1024;
     int stages = (int)((220 * 1024 - fixed) / GSLICE_BYTES);
-    stages = std::min(stages, 6);
+    stages = std::min(stages, 8);
     if (stages < 2) return fail(LK_ERANGE, "gemm search: rows too wide for the resident query tile");
     const size_t smem = fixed + (size_t)stages * GSLICE_BYTES;
     cudaError_t e = cudaFuncSetAttribute((const void *)k_gemm_i8_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
