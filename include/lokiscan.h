@@ -248,6 +248,25 @@ LK_API int lk_scan_i8_prealloc(int device, const int8_t *d_codes, int64_t n, int
 LK_API int lk_prescreen_pairs(const float *vecs, int64_t n, int dim, float threshold, int device,
                               int32_t *near, int32_t *count, uint8_t *overflow);
 
+/* ---- face-clustering candidate x seed scores ---------------------------------- */
+
+/* Replaces the dot products of scoreAgainstSeeds (media-server/tasks/face_cluster.go:1315-1462):
+ * for every candidate (n_cand unit vectors of dim floats, row-major) the seeds (n_seeds unit
+ * vectors) whose float32 dot with it is >= min_score, in ascending seed order, with the
+ * scores.  The caller passes min_score = threshold - corroborationSlack (:1417) and runs the
+ * reference's decision logic over the lists.
+ * Arithmetic follows the reference bit for bit: candidates are scored four at a time with
+ * dot4 (:939-967), the last 1-3 candidates of each worker chunk with dotf (:908-925).
+ *   chunk      candidates per worker chunk of the reference, (n + workers - 1) / workers
+ *              (:1349-1350); 0 = all candidates in one chunk
+ *   row_start  n_cand + 1 offsets: candidate i's pairs are out_seed/out_score[row_start[i] .. row_start[i+1])
+ *   cap        pairs out_seed / out_score can hold
+ *   out_total  pairs that reach the floor; when it exceeds cap nothing is written, the
+ *              call returns LK_ERANGE and can be repeated with room for out_total pairs */
+LK_API int lk_seed_scores(const float *cands, int64_t n_cand, const float *seeds, int64_t n_seeds, int dim,
+                          float min_score, int64_t chunk, int device, int64_t *row_start, int32_t *out_seed,
+                          float *out_score, int64_t cap, int64_t *out_total);
+
 /* ---- statistics ----------------------------------------------------------- */
 
 typedef struct {

@@ -94,6 +94,7 @@ _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64,
 _sig("lk_stats", _int, _vp, C.POINTER(lk_stats_t))
 _sig("lk_index_set_batch_mode", _int, _vp, _int)
 _sig("lk_prescreen_pairs", _int, _vp, _i64, _int, C.c_float, _int, _vp, _vp, _vp)
+_sig("lk_seed_scores", _int, _vp, _i64, _vp, _i64, _int, C.c_float, _i64, _int, _vp, _vp, _vp, _i64, _vp)
 _sig("lk_scan_i8_prealloc", _int, _int, _vp, _i64, _int, _i64, _vp, _vp, C.c_float, _int, _vp, _vp, _vp, _vp, _vp)
 LK_PREALLOC_MAX_K = 128
 
@@ -353,3 +354,27 @@ def prescreen_pairs(vecs, threshold: float, device: int = 0):
     over = np.zeros(max(n, 1), np.uint8)
     check(lib.lk_prescreen_pairs(ptr(v), n, dim, C.c_float(threshold), int(device), ptr(near), ptr(count), ptr(over)))
     return near[:n], count[:n], over[:n].astype(bool)
+
+
+def seed_scores(cands, seeds, min_score: float, chunk: int = 0, device: int = 0):
+    """Candidate x seed scores of face clustering at or above `min_score`:
+    -> (row_start[n_cand + 1] int64, seed[total] int32 ascending per candidate, score[total] float32)."""
+    c = np.ascontiguousarray(cands, dtype=np.float32)
+    s = np.ascontiguousarray(seeds, dtype=np.float32)
+    n_cand, n_seeds = c.shape[0], s.shape[0]
+    dim = c.shape[1] if c.ndim == 2 and n_cand else (s.shape[1] if s.ndim == 2 and n_seeds else 1)
+    row_start = np.zeros(n_cand + 1, np.int64)
+    total = _i64(0)
+    cap = max(1024, 8 * n_cand)
+    for _ in range(2):  # a second call when the first guess at the output size was too small
+        out_seed = np.empty(cap, np.int32)
+        out_score = np.empty(cap, np.float32)
+        st = lib.lk_seed_scores(ptr(c), n_cand, ptr(s), n_seeds, int(dim), C.c_float(min_score), int(chunk), int(device),
+                                ptr(row_start), ptr(out_seed), ptr(out_score), int(cap), C.byref(total))
+        if st == LK_ERANGE and total.value > cap:
+            cap = int(total.value)
+            continue
+        check(st)
+        break
+    n = int(total.value)
+    return row_start, out_seed[:n].copy(), out_score[:n].copy()

@@ -98,6 +98,12 @@ def lib():
     for fn in (L.orc_prescreen, L.orc_prescreen_bruteforce):
         fn.argtypes = [_f32p, C.c_int, C.c_int, C.c_float, _i32p, _i32p, _u8p]
         fn.restype = None
+    L.orc_seed_scores.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, _f32p]
+    L.orc_seed_scores.restype = None
+    L.orc_seed_scores_single.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, _f32p]
+    L.orc_seed_scores_single.restype = None
+    L.orc_dot32.argtypes = [_f32p, _f32p, C.c_int]
+    L.orc_dot32.restype = C.c_float
     _lib = L
     return L
 
@@ -327,3 +333,23 @@ def prescreen(vecs, threshold: float, brute_force: bool = False):
     if n:
         fn(v, n, d, float(threshold), near.reshape(-1), count, over)
     return near[:n], count[:n], over[:n].astype(bool)
+
+
+# ---- face-clustering candidate x seed scores (media-server/tasks/face_cluster.go:1315-1462) ----
+
+def seed_scores(cands, seeds, chunk: int = 0, grouped: bool = True) -> np.ndarray:
+    """Dense n_cand x n_seeds float32 scores: four candidates at a time within worker chunks of
+    `chunk` candidates (`grouped`), or every pair one at a time."""
+    c, s = _f32(cands), _f32(seeds)
+    out = np.zeros((c.shape[0], s.shape[0]), np.float32)
+    if c.shape[0] and s.shape[0]:
+        if grouped:
+            lib().orc_seed_scores(c, c.shape[0], s, s.shape[0], c.shape[1], int(chunk), out.reshape(-1))
+        else:
+            lib().orc_seed_scores_single(c, c.shape[0], s, s.shape[0], c.shape[1], out.reshape(-1))
+    return out
+
+
+def dot32(a, b) -> np.float32:
+    a, b = _f32(a), _f32(b)
+    return np.float32(lib().orc_dot32(a, b, a.size))

@@ -559,6 +559,45 @@ ORC_API void orc_prescreen(const float *v, int n, int d, float threshold, int32_
     free(tmp);
 }
 
+/* Every candidate against every seed, float32, in the reference's two summation orders:
+ * inside each worker chunk candidates go four at a time through dot4 and the last one to three
+ * through dotf.  out is n_cand x n_seeds.  chunk = candidates per worker chunk (0 = one chunk).
+ * Follows media-server/tasks/face_cluster.go:1349-1360 and :1375-1400. */
+ORC_API void orc_seed_scores(const float *cands, int n_cand, const float *seeds, int n_seeds, int d, int chunk,
+                             float *out) {
+    if (chunk <= 0) chunk = n_cand;
+    for (int lo = 0; lo < n_cand; lo += chunk) {
+        int hi = lo + chunk < n_cand ? lo + chunk : n_cand;
+        int base = lo;
+        for (; base + 4 <= hi; base += 4) {
+            for (int k = 0; k < n_seeds; k++) {
+                float s[4];
+                dot4(cands + (size_t)base * d, cands + (size_t)(base + 1) * d, cands + (size_t)(base + 2) * d,
+                     cands + (size_t)(base + 3) * d, seeds + (size_t)k * d, d, s);
+                for (int r = 0; r < 4; r++) out[(size_t)(base + r) * n_seeds + k] = s[r];
+            }
+        }
+        for (; base < hi; base++)
+            for (int k = 0; k < n_seeds; k++)
+                out[(size_t)base * n_seeds + k] = orc_dotf(cands + (size_t)base * d, seeds + (size_t)k * d, d);
+    }
+}
+
+/* The one-candidate-at-a-time scores the reference's own test compares the grouped version
+ * with (media-server/tasks/face_score_kernel_test.go:17-44): dotf for every pair. */
+ORC_API void orc_seed_scores_single(const float *cands, int n_cand, const float *seeds, int n_seeds, int d, float *out) {
+    for (int i = 0; i < n_cand; i++)
+        for (int k = 0; k < n_seeds; k++)
+            out[(size_t)i * n_seeds + k] = orc_dotf(cands + (size_t)i * d, seeds + (size_t)k * d, d);
+}
+
+/* float64-accumulated dot rounded once (media-server/tasks/face_cluster.go:890-896). */
+ORC_API float orc_dot32(const float *a, const float *b, int n) {
+    double acc = 0.0;
+    for (int i = 0; i < n; i++) acc += (double)a[i] * (double)b[i];
+    return (float)acc;
+}
+
 /* The definition the reference's own test checks the prescreen against
  * (media-server/tasks/face_cluster_perf_test.go:52-81): every j < i with dotf >= threshold. */
 ORC_API void orc_prescreen_bruteforce(const float *v, int n, int d, float threshold, int32_t *near,

@@ -38,3 +38,44 @@ def phash_set(n: int, seed: int, dup_frac: float = 0.1, max_flips: int = 6) -> n
     allh = np.concatenate([base, dup])
     rng.shuffle(allh)
     return allh
+
+
+def seed_scoring_case(n_cand: int, n_seed: int, people: int, dims: int, vetoes: bool, cannot_links: bool,
+                      users: bool, seed: int):
+    """The scenario shape of the reference's grouped-vs-one-at-a-time test
+    (media-server/tasks/face_score_kernel_test.go:80-150) over this repo's own seeded generator:
+    people with tight seed clouds (spread 0.02), every third candidate near a person's centre
+    (spread 0.03), the rest junk; optional vetoes (every 4th candidate from 1), cannot-links
+    (every 6th from 2) and user seeds (every 5th)."""
+    rng = np.random.default_rng(seed)
+
+    def unit(v):
+        v = v.astype(np.float32)
+        return (v / np.sqrt(np.sum(v.astype(np.float64) ** 2))).astype(np.float32)
+
+    centres = [unit(rng.standard_normal(dims)) for _ in range(people)]
+    seed_ids = [i + 1 for i in range(n_seed)]
+    seed_person = [i % people + 1 for i in range(n_seed)]
+    seed_user = [bool(users and i % 5 == 0) for i in range(n_seed)]
+    seed_vecs = np.stack([unit(centres[seed_person[i] - 1] + 0.02 * rng.standard_normal(dims)) for i in range(n_seed)])
+    cand_ids = [1_000_000 + i for i in range(n_cand)]
+    cand_vecs = np.stack([unit(centres[i % people] + 0.03 * rng.standard_normal(dims)) if i % 3 == 0
+                          else unit(rng.standard_normal(dims)) for i in range(n_cand)])
+    veto = {cand_ids[i]: {i % people + 1} for i in range(1, n_cand, 4)} if vetoes else {}
+    cannot = {cand_ids[i]: {seed_ids[(i * 3) % n_seed]} for i in range(2, n_cand, 6)} if cannot_links else {}
+    return dict(cand_ids=cand_ids, cand_vecs=cand_vecs, seed_ids=seed_ids, seed_vecs=seed_vecs,
+                seed_person=seed_person, seed_user=seed_user, vetoes=veto, cannot=cannot)
+
+
+# (name, n_cand, n_seed, people, dims, threshold, vetoes, cannot-links, user seeds): the reference's table
+SEED_SCORING_CASES = [
+    ("plain", 200, 500, 10, 64, 0.42, False, False, False),
+    ("candidate count not a multiple of the group width", 203, 501, 7, 64, 0.42, False, False, False),
+    ("seed count straddling the chunk boundary", 64, 257, 5, 64, 0.42, False, False, False),
+    ("with user seeds", 200, 500, 8, 64, 0.42, False, False, True),
+    ("with vetoes", 200, 500, 8, 64, 0.42, True, False, True),
+    ("with cannot-links", 200, 500, 8, 64, 0.42, False, True, True),
+    ("everything at once, low threshold", 300, 800, 12, 32, 0.20, True, True, True),
+    ("single candidate", 1, 300, 4, 64, 0.42, True, True, True),
+    ("fewer candidates than the group width", 3, 300, 4, 64, 0.42, True, True, True),
+]
