@@ -54,20 +54,24 @@ __global__ void __launch_bounds__(PTHREADS) k_prescreen_pairs(const float *__res
             for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int m = 0; m < 4; ++m) acc[r][c][m] = 0.0f;
+        // this thread's 4 floats of the staging step (zero past the end of a row or of the matrix):
+        // fetched one step ahead, so the L2 latency hides behind the arithmetic of the step before
+        const int lrow = tid >> 2, lkk = (tid & 3) * 4;
+        const float *ap = (i0 + lrow < n) ? v + (size_t)(i0 + lrow) * ld + lkk : nullptr;
+        const float *bp = (j0 + lrow < n) ? v + (size_t)(j0 + lrow) * ld + lkk : nullptr;
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 a_next = (ap && lkk < ld) ? *reinterpret_cast<const float4 *>(ap) : zero4;
+        float4 b_next = (bp && lkk < ld) ? *reinterpret_cast<const float4 *>(bp) : zero4;
         for (int k0 = 0; k0 < dim; k0 += PK) {
             __syncthreads();
-            // stage 64 x 16 floats of both sides (zero past the end of a row or of the matrix)
-            {
-                const int row = tid >> 2, kk = (tid & 3) * 4;
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                if (k0 + kk < ld) {
-                    if (i0 + row < n) a = *reinterpret_cast<const float4 *>(v + (size_t)(i0 + row) * ld + k0 + kk);
-                    if (j0 + row < n) b = *reinterpret_cast<const float4 *>(v + (size_t)(j0 + row) * ld + k0 + kk);
-                }
-                *reinterpret_cast<float4 *>(&As[row][kk]) = a;
-                *reinterpret_cast<float4 *>(&Bs[row][kk]) = b;
-            }
+            *reinterpret_cast<float4 *>(&As[lrow][lkk]) = a_next;
+            *reinterpret_cast<float4 *>(&Bs[lrow][lkk]) = b_next;
             __syncthreads();
+            {
+                const int kn = k0 + PK + lkk;
+                a_next = (ap && kn < ld) ? *reinterpret_cast<const float4 *>(ap + k0 + PK) : zero4;
+                b_next = (bp && kn < ld) ? *reinterpret_cast<const float4 *>(bp + k0 + PK) : zero4;
+            }
 #pragma unroll
             for (int g = 0; g < PK; g += 4) {
                 if (k0 + g >= dim) break;
