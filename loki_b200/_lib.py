@@ -247,8 +247,8 @@ class DeviceIndex:
         self._comm = comm
 
     def set_batch_mode(self, tensor_cores: bool):
-        """Batches of >= 32 queries on an int8 index: tensor-core matrix product (True, default)
-        or consecutive single-query scans (False); results are identical."""
+        """Batches of queries (>= 32 on an int8 index, >= 3 on a float32 index): tensor-core
+        kernels (True, default) or consecutive single-query scans (False)."""
         check(lib.lk_index_set_batch_mode(self._h, 1 if tensor_cores else 0))
 
     def set_shard_base(self, base: int):

@@ -21,6 +21,7 @@
 #include "build.cuh"
 #include "comm.hpp"
 #include "gemm.cuh"
+#include "multi.cuh"
 #include "hostmath.hpp"
 #include "index_internal.cuh"
 #include "lk_common.cuh"
@@ -268,6 +269,78 @@ static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, 
     m.nq = nq;
     m.k = k_eff;
     m.type = SCAN_I8;
+    m.out_ids = idx->res.d_ids();
+    m.out_scores = idx->res.d_scores();
+    m.out_iscores = idx->res.d_iscores();
+    m.out_count = idx->res.d_counts();
+    LK_TRY(merge_launch(m, idx->stream));
+    idx->aux_launches++;
+    int h_err = 0;
+    LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaMemcpyAsync(&h_err, d_err, 4, cudaMemcpyDeviceToHost, idx->stream));
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
+    if (h_err != 0) {
+        LK_CUDA(cudaMemsetAsync(d_err, 0, 4, idx->stream));
+        return fail(LK_ETIMEOUT, "the batched search kernel gave up on a bounded wait; results are not valid");
+    }
+    return unpack_results(idx->res, nq, k_user, k_eff, 1, out_ids, out_scores, out_iscores, out_counts);
+}
+
+// A batch of queries on a float32 index: 8 queries per pass over the corpus on the float64
+// tensor-core path (multi_mma.cu), then one merge of the CTAs' lists per query.
+static int search_multi_f32(lk_index *idx, const float *queries, int nq, int scoring, int k_user, int k_eff,
+                            int64_t *out_ids, float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+    const int grid = multi_grid(idx->len, idx->sm_count);
+    const size_t e = (size_t)nq * k_eff;
+    // device: prepared queries | cq | list bases (zeros) | lists [grid][nq][k] | merge scratch
+    const size_t q_bytes = (size_t)round_up((int64_t)nq * idx->qbytes, 256);
+    const size_t cq_bytes = (size_t)round_up((int64_t)nq * 4, 256);
+    const size_t base_bytes = (size_t)round_up((int64_t)grid * 8, 256);
+    const size_t list_bytes = (size_t)grid * e * 8;
+    LK_TRY(idx->d_query.reserve(q_bytes + cq_bytes + base_bytes + 2 * list_bytes));
+    LK_TRY(idx->h_query.reserve(q_bytes + cq_bytes));
+    LK_TRY(idx->res.shape(nq, k_eff, 1));
+    unsigned char *hq = (unsigned char *)idx->h_query.p;
+    float *hcq = reinterpret_cast<float *>(hq + q_bytes);
+    bool centered = false;
+    for (int q = 0; q < nq; ++q) {
+        float qscale = 0.0f;
+        const bool c = prepare_query(idx, queries + (size_t)q * idx->dim, scoring, hq + (size_t)q * idx->qbytes, &hcq[q], &qscale);
+        if (q == 0) centered = c;
+    }
+    unsigned char *dq = (unsigned char *)idx->d_query.p;
+    LK_CUDA(cudaMemcpyAsync(dq, hq, q_bytes + cq_bytes, cudaMemcpyHostToDevice, idx->stream));
+    LK_CUDA(cudaMemsetAsync(dq + q_bytes + cq_bytes, 0, base_bytes, idx->stream));
+    unsigned long long *d_lists = (unsigned long long *)(dq + q_bytes + cq_bytes + base_bytes);
+    int *d_err = (int *)(idx->d_ticket + 1);
+    for (int q0 = 0; q0 < nq; q0 += kMultiQueries) {
+        MultiArgs a;
+        a.rows = idx->d_rows;
+        a.ld = idx->ld;
+        a.n = idx->len;
+        a.queries = reinterpret_cast<const float *>(dq + (size_t)q0 * idx->qbytes);
+        a.cq = reinterpret_cast<const float *>(dq + q_bytes) + q0;
+        a.cnorm = centered ? idx->d_cnorm : nullptr;
+        a.nq = std::min(kMultiQueries, nq - q0);
+        a.q0 = q0;
+        a.nq_total = nq;
+        a.k = k_eff;
+        a.lists = d_lists;
+        a.error = d_err;
+        LK_TRY(multi_launch(a, grid, idx->stream));
+        idx->aux_launches++;
+    }
+    MergeArgs m;
+    m.keys = d_lists;
+    m.payload = nullptr;
+    m.qscales = nullptr;
+    m.scales = nullptr;
+    m.scratch = d_lists + (size_t)grid * e;
+    m.list_base = (const long long *)(dq + q_bytes + cq_bytes);
+    m.lists = grid;
+    m.nq = nq;
+    m.k = k_eff;
+    m.type = SCAN_F32;
     m.out_ids = idx->res.d_ids();
     m.out_scores = idx->res.d_scores();
     m.out_iscores = idx->res.d_iscores();
@@ -576,6 +649,12 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     if (idx->store == LK_I8 && nq >= GEMM_MIN_QUERIES && !filtered && !sharded && gemm_supported(idx->ld, k_eff) &&
         idx->len >= 4096 && !idx->no_gemm) {
         LK_TRY(search_gemm(idx, queries, nq, k, k_eff, out_ids, out_scores, out_iscores, out_counts));
+        idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        return LK_OK;
+    }
+    if (idx->store == LK_F32 && nq >= kMultiMinQueries && !filtered && !sharded && idx->len >= 8192 && !idx->no_gemm &&
+        multi_supported(idx->ld, k_eff) && (long long)nq * k_eff <= (1 << 20)) {
+        LK_TRY(search_multi_f32(idx, queries, nq, scoring, k, k_eff, out_ids, out_scores, out_iscores, out_counts));
         idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
         return LK_OK;
     }
