@@ -150,8 +150,9 @@ LK_API int lk_search_shared(lk_index *idx, const float *pos, const float *posw, 
  * mode 1 (default): 32 or more queries on an LK_I8 index as one int8 tensor-core matrix
  * product with the top-k fused into its epilogue; 3 or more queries on an LK_F32 index of
  * 8,192+ rows eight to a pass over the corpus on the float64 tensor-core path.
- * mode 0: consecutive single-query scans.  int8 results are identical; float32 scores are
- * identical and hit lists can differ only between rows whose scores tie to the last bits. */
+ * mode 0: consecutive single-query scans.  int8 results are identical.  float32 scores come
+ * from the same arithmetic (exact products, float64 accumulation, one rounding) summed in a
+ * different order, so hit lists can differ only between rows whose scores tie to the last bits. */
 LK_API int lk_index_set_batch_mode(lk_index *idx, int mode);
 
 /* ---- device-resident queries (throughput measurement, pipelined callers) -- */
