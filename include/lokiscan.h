@@ -80,6 +80,8 @@ LK_API int lk_index_reserve(lk_index *idx, int64_t n);
 /* Replaces Len() (media-server/embedindex/embedindex.go:219). */
 LK_API int64_t lk_index_len(const lk_index *idx);
 LK_API int lk_index_dim(const lk_index *idx);
+/* Storage type (LK_F32 / LK_F16 / LK_I8) and whether the index was created centered. */
+LK_API int lk_index_kind(const lk_index *idx, int *store, int *centered);
 
 /* Replaces Add (media-server/embedindex/embedindex.go:176-194) for n rows at once:
  * rows[i] (dim floats each, raw model output) is L2-normalised on the device
@@ -145,6 +147,16 @@ LK_API int lk_search_shared(lk_index *idx, const float *pos, const float *posw, 
                             float beta, float lambda, int k, int scoring,
                             const int32_t *allow_slots, int64_t n_allow,
                             int64_t *out_ids, float *out_scores, int32_t *out_count);
+
+/* On-disk cache of a built index, replacing the rebuild from SQLite BLOBs at every start
+ * (media-server/tasks/embed_task.go:189-210: LoadAllEmbeddings, then one Add per row).  The file
+ * holds the index as it sits in device memory (normalised or quantised rows, scales, the
+ * centering state a search would see) behind a 128-byte header with a checksum.  `tag` is the
+ * caller's key, e.g. a hash of model name and row count: lk_index_load refuses a file written
+ * under another tag (LK_EINVAL), as it does a truncated, extended or damaged one.  Slot order
+ * is preserved; the caller keeps its own path list in the same order. */
+LK_API int lk_index_save(lk_index *idx, const char *path, uint64_t tag);
+LK_API int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out);
 
 /* How lk_search runs a batch of queries (no allow-list, k <= 256, index not sharded).
  * mode 1 (default): 32 or more queries on an LK_I8 index as one int8 tensor-core matrix

@@ -44,6 +44,12 @@ LK_API int lkx_delete(lkx_index *x, const char *path);
 /* Len (media-server/embedindex/embedindex.go:219). */
 LK_API int64_t lkx_len(const lkx_index *x);
 
+/* On-disk cache of the built index: lk_index_save's file plus `<path>.paths` with the paths in
+ * slot order.  Replaces BuildIndexFromDB's rebuild at start (media-server/tasks/embed_task.go:189-210)
+ * whenever the caller's tag (model + row count) still matches. */
+LK_API int lkx_save(lkx_index *x, const char *path, uint64_t tag);
+LK_API int lkx_load(const char *path, uint64_t tag, int device, lkx_index **out);
+
 /* Search / SearchFiltered / SearchScored (media-server/embedindex/embedindex.go:308-328).
  * has_allow = 0 is Go's nil allow set (no restriction); has_allow = 1 restricts to
  * the n_allow paths in `allow` (unknown paths are skipped; an empty or fully

@@ -67,6 +67,9 @@ _sig("lk_index_destroy", _int, _vp)
 _sig("lk_index_reserve", _int, _vp, _i64)
 _sig("lk_index_len", _i64, _vp)
 _sig("lk_index_dim", _int, _vp)
+_sig("lk_index_kind", _int, _vp, _vp, _vp)
+_sig("lk_index_save", _int, _vp, C.c_char_p, C.c_uint64)
+_sig("lk_index_load", _int, C.c_char_p, C.c_uint64, _int, C.POINTER(_vp))
 _sig("lk_index_upsert_f32", _int, _vp, _i64, _i64, _vp)
 _sig("lk_index_upsert_f32_device", _int, _vp, _i64, _i64, _vp)
 _sig("lk_index_swap_remove", _int, _vp, _i64)
@@ -137,6 +140,23 @@ class DeviceIndex:
         if getattr(self, "_h", None) and lib is not None:  # lib is None during interpreter shutdown
             lib.lk_index_destroy(self._h)
             self._h = None
+
+    def save(self, path: str, tag: int = 0):
+        """Write the built index (rows as stored, scales, centering state) to `path`."""
+        check(lib.lk_index_save(self._h, os.fsencode(path), C.c_uint64(int(tag))))
+
+    @classmethod
+    def load(cls, path: str, tag: int = 0, device: int = 0) -> "DeviceIndex":
+        """Read an index written by :meth:`save`; raises when tag, size or checksum do not match."""
+        h = _vp()
+        check(lib.lk_index_load(os.fsencode(path), C.c_uint64(int(tag)), int(device), C.byref(h)))
+        self = cls.__new__(cls)
+        self._h = h
+        store, centered = _int(0), _int(0)
+        check(lib.lk_index_kind(h, C.byref(store), C.byref(centered)))
+        self.dim, self.store, self.centered, self.device = int(lib.lk_index_dim(h)), store.value, bool(centered.value), int(device)
+        self._comm = None
+        return self
 
     __del__ = close
 

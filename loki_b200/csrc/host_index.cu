@@ -4,6 +4,7 @@
 // path table, the slot map and the ordering of ties by path.
 #include <algorithm>
 #include <new>
+#include <cstdio>
 #include <string>
 #include <unordered_map>
 #include <unordered_set>
@@ -261,5 +262,68 @@ float lkx_hits_score(const lkx_hits *h, int64_t i) {
     return (h && i >= 0 && i < (int64_t)h->score.size()) ? h->score[(size_t)i] : 0.0f;
 }
 void lkx_hits_free(lkx_hits *h) { delete h; }
+
+
+// ---- on-disk cache: the device-side file of lk_index_save plus the paths in slot order ----
+
+int lkx_save(lkx_index *x, const char *path, uint64_t tag) {
+    if (!x || !path) return fail(LK_EINVAL, "lkx_save: bad argument");
+    if (!x->dev) return fail(LK_EINVAL, "lkx_save: the index is empty");
+    LK_TRY(lk_index_save(x->dev, path, tag));
+    const std::string names = std::string(path) + ".paths", tmp = names + ".tmp";
+    FILE *f = fopen(tmp.c_str(), "wb");
+    if (!f) return fail(LK_EINVAL, "lkx_save: cannot create " + tmp);
+    bool ok = true;
+    const uint64_t n = x->paths.size();
+    ok = ok && fwrite(&n, 8, 1, f) == 1;
+    for (const std::string &p : x->paths) {
+        const uint32_t len = (uint32_t)p.size();
+        ok = ok && fwrite(&len, 4, 1, f) == 1 && (len == 0 || fwrite(p.data(), 1, len, f) == len);
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok || rename(tmp.c_str(), names.c_str()) != 0) {
+        remove(tmp.c_str());
+        return fail(LK_EINVAL, "lkx_save: writing " + names + " failed");
+    }
+    return LK_OK;
+}
+
+int lkx_load(const char *path, uint64_t tag, int device, lkx_index **out) {
+    if (!path || !out) return fail(LK_EINVAL, "lkx_load: bad argument");
+    *out = nullptr;
+    lk_index *dev = nullptr;
+    LK_TRY(lk_index_load(path, tag, device, &dev));
+    lkx_index *x = new (std::nothrow) lkx_index();
+    if (!x) {
+        lk_index_destroy(dev);
+        return fail(LK_ENOMEM, "lkx_load: out of host memory");
+    }
+    x->dev = dev;
+    x->dim = lk_index_dim(dev);
+    x->device = device;
+    lk_index_kind(dev, &x->store, &x->centered);
+    const std::string names = std::string(path) + ".paths";
+    FILE *f = fopen(names.c_str(), "rb");
+    bool ok = f != nullptr;
+    uint64_t n = 0;
+    ok = ok && fread(&n, 8, 1, f) == 1 && (int64_t)n == lk_index_len(dev);
+    for (uint64_t i = 0; ok && i < n; ++i) {
+        uint32_t len = 0;
+        ok = fread(&len, 4, 1, f) == 1 && len < (1u << 20);
+        std::string p(len, '\0');
+        ok = ok && (len == 0 || fread(&p[0], 1, len, f) == len);
+        if (ok) {
+            ok = x->slot.emplace(p, (int64_t)i).second;  // a path can own one slot only
+            x->paths.emplace_back(std::move(p));
+        }
+    }
+    if (f) fclose(f);
+    if (!ok) {
+        lkx_free(x);
+        return fail(LK_EINVAL, "lkx_load: " + names + " is missing or does not match the cached rows");
+    }
+    *out = x;
+    return LK_OK;
+}
 
 }  // extern "C"

@@ -20,6 +20,8 @@
 #include "../../include/lokiscan.h"
 #include "build.cuh"
 #include "comm.hpp"
+#include <cstdio>
+
 #include "gemm.cuh"
 #include "multi.cuh"
 #include "hostmath.hpp"
@@ -537,6 +539,12 @@ int lk_index_reserve(lk_index *idx, int64_t n) {
 }
 
 int64_t lk_index_len(const lk_index *idx) { return idx ? idx->len : 0; }
+int lk_index_kind(const lk_index *idx, int *store, int *centered) {
+    if (!idx) return fail(LK_EINVAL, "lk_index_kind: idx is NULL");
+    if (store) *store = idx->store;
+    if (centered) *centered = idx->centered;
+    return LK_OK;
+}
 int lk_index_dim(const lk_index *idx) { return idx ? idx->dim : 0; }
 
 int lk_index_upsert_f32_device(lk_index *idx, int64_t first_slot, int64_t n, const float *d_rows) {
@@ -935,6 +943,173 @@ int lk_stats(lk_index *idx, lk_stats_t *out) {
     out->last_search_ms = idx->last_search_ms;
     out->grid = idx->grid;
     out->sm_count = idx->sm_count;
+    return LK_OK;
+}
+
+}  // extern "C"
+
+// ---- on-disk cache of a built index ----------------------------------------------------
+// The reference rebuilds its index from SQLite BLOBs at every start, one Add per row
+// (media-server/tasks/embed_task.go:189-210, media-server/media/embedding.go:114-136); at
+// millions of rows that rebuild dominates the time to the first query.  A built index is
+// therefore written out as it sits in HBM (normalised / quantised rows, scales, centering
+// state) and read back with plain copies.  The caller's tag (e.g. a hash of model name and
+// row count) must match on load, as must a checksum of the payload.
+
+namespace {
+
+struct CacheHeader {  // 128 bytes, little-endian like the machine
+    char magic[8];    // "LKIDX001"
+    int32_t dim, store, centered, center_live;
+    int64_t len, ld, n_centered;
+    uint64_t tag, checksum;
+    double mu_n2;
+    unsigned char pad[56];
+};
+static_assert(sizeof(CacheHeader) == 128, "cache header layout");
+
+// word-wise FNV-1a-style hash: fast enough for gigabytes, sensitive to any flipped bit
+struct Hasher {
+    uint64_t h = 0xcbf29ce484222325ull;
+    void add(const void *p, size_t n) {
+        const unsigned char *b = (const unsigned char *)p;
+        size_t i = 0;
+        for (; i + 8 <= n; i += 8) {
+            uint64_t w;
+            memcpy(&w, b + i, 8);
+            h = (h ^ w) * 0x100000001b3ull;
+            h ^= h >> 29;
+        }
+        for (; i < n; ++i) h = (h ^ b[i]) * 0x100000001b3ull;
+    }
+};
+
+constexpr size_t kCacheChunk = 32u << 20;
+
+// device -> file (through pinned memory), hashing on the way
+int dump_device(lk_index *idx, const void *d, size_t bytes, FILE *f, lk::PinnedBuf &pin, Hasher &hs) {
+    for (size_t off = 0; off < bytes; off += kCacheChunk) {
+        const size_t m = std::min(kCacheChunk, bytes - off);
+        LK_CUDA(cudaMemcpyAsync(pin.p, (const unsigned char *)d + off, m, cudaMemcpyDeviceToHost, idx->stream));
+        LK_CUDA(cudaStreamSynchronize(idx->stream));
+        hs.add(pin.p, m);
+        if (fwrite(pin.p, 1, m, f) != m) return fail(LK_EINVAL, "lk_index_save: write failed");
+    }
+    return 0;
+}
+int fill_device(lk_index *idx, void *d, size_t bytes, FILE *f, lk::PinnedBuf &pin, Hasher &hs) {
+    for (size_t off = 0; off < bytes; off += kCacheChunk) {
+        const size_t m = std::min(kCacheChunk, bytes - off);
+        if (fread(pin.p, 1, m, f) != m) return fail(LK_EINVAL, "lk_index_load: the file is shorter than its header says");
+        hs.add(pin.p, m);
+        LK_CUDA(cudaMemcpyAsync((unsigned char *)d + off, pin.p, m, cudaMemcpyHostToDevice, idx->stream));
+        LK_CUDA(cudaStreamSynchronize(idx->stream));
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
+    if (!idx || !path) return fail(LK_EINVAL, "lk_index_save: bad argument");
+    if (idx->comm) return fail(LK_EINVAL, "lk_index_save: save each shard from its own unsharded handle");
+    LK_TRY(use_device(idx));
+    LK_TRY(maybe_recenter(idx));  // the cache holds the state a search would see
+    const std::string tmp = std::string(path) + ".tmp";
+    FILE *f = fopen(tmp.c_str(), "wb");
+    if (!f) return fail(LK_EINVAL, std::string("lk_index_save: cannot create ") + tmp);
+    lk::PinnedBuf pin;
+    int st = pin.reserve(kCacheChunk);
+    CacheHeader h;
+    memset(&h, 0, sizeof(h));
+    memcpy(h.magic, "LKIDX001", 8);
+    h.dim = idx->dim;
+    h.store = idx->store;
+    h.centered = idx->centered;
+    h.center_live = idx->center_live ? 1 : 0;
+    h.len = idx->len;
+    h.ld = idx->ld;
+    h.n_centered = idx->n_centered;
+    h.tag = tag;
+    h.mu_n2 = idx->mu_n2;
+    Hasher hs;
+    if (st == 0 && fwrite(&h, 1, sizeof(h), f) != sizeof(h)) st = fail(LK_EINVAL, "lk_index_save: write failed");
+    if (st == 0 && idx->len > 0) st = dump_device(idx, idx->d_rows, (size_t)idx->len * idx->ld, f, pin, hs);
+    if (st == 0 && idx->len > 0 && idx->d_scales) st = dump_device(idx, idx->d_scales, (size_t)idx->len * 4, f, pin, hs);
+    if (st == 0 && idx->centered) {
+        st = dump_device(idx, idx->d_sum, sizeof(double) * idx->dim, f, pin, hs);
+        if (st == 0 && idx->center_live) {
+            hs.add(idx->h_mu.data(), sizeof(float) * idx->dim);
+            if (fwrite(idx->h_mu.data(), sizeof(float), (size_t)idx->dim, f) != (size_t)idx->dim)
+                st = fail(LK_EINVAL, "lk_index_save: write failed");
+            if (st == 0 && idx->len > 0) st = dump_device(idx, idx->d_cnorm, (size_t)idx->len * 4, f, pin, hs);
+        }
+    }
+    if (st == 0) {
+        h.checksum = hs.h;
+        if (fseek(f, 0, SEEK_SET) != 0 || fwrite(&h, 1, sizeof(h), f) != sizeof(h)) st = fail(LK_EINVAL, "lk_index_save: write failed");
+    }
+    if (fclose(f) != 0 && st == 0) st = fail(LK_EINVAL, "lk_index_save: close failed");
+    pin.release();
+    if (st == 0 && rename(tmp.c_str(), path) != 0) st = fail(LK_EINVAL, std::string("lk_index_save: cannot rename to ") + path);
+    if (st != 0) remove(tmp.c_str());
+    return st;
+}
+
+int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out) {
+    if (!path || !out) return fail(LK_EINVAL, "lk_index_load: bad argument");
+    *out = nullptr;
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(LK_EINVAL, std::string("lk_index_load: cannot open ") + path);
+    CacheHeader h;
+    int st = 0;
+    if (fread(&h, 1, sizeof(h), f) != sizeof(h) || memcmp(h.magic, "LKIDX001", 8) != 0)
+        st = fail(LK_EINVAL, "lk_index_load: not an index cache of this version");
+    else if (h.tag != tag)
+        st = fail(LK_EINVAL, "lk_index_load: the cache was written for another tag (model or row count changed)");
+    else if (h.len < 0 || h.len > 0xfffffff0ll || h.dim < 1 || h.dim > LK_MAX_DIM)
+        st = fail(LK_EINVAL, "lk_index_load: implausible header");
+    lk_index *idx = nullptr;
+    if (st == 0) st = lk_index_create(h.dim, h.store, h.centered, device, &idx);
+    if (st == 0 && idx->ld != h.ld) st = fail(LK_EINVAL, "lk_index_load: row stride of the cache does not match this library");
+    lk::PinnedBuf pin;
+    if (st == 0) st = pin.reserve(kCacheChunk);
+    Hasher hs;
+    if (st == 0 && h.len > 0) {
+        st = grow_rows(idx, h.len);
+        if (st == 0) st = fill_device(idx, idx->d_rows, (size_t)h.len * idx->ld, f, pin, hs);
+        if (st == 0 && idx->d_scales) st = fill_device(idx, idx->d_scales, (size_t)h.len * 4, f, pin, hs);
+    }
+    if (st == 0 && idx->centered) {
+        st = fill_device(idx, idx->d_sum, sizeof(double) * idx->dim, f, pin, hs);
+        if (st == 0 && h.center_live) {
+            idx->h_mu.assign((size_t)idx->dim, 0.0f);
+            if (fread(idx->h_mu.data(), sizeof(float), (size_t)idx->dim, f) != (size_t)idx->dim)
+                st = fail(LK_EINVAL, "lk_index_load: the file is shorter than its header says");
+            if (st == 0) {
+                hs.add(idx->h_mu.data(), sizeof(float) * idx->dim);
+                cudaError_t e = cudaMemcpyAsync(idx->d_mu, idx->h_mu.data(), sizeof(float) * idx->dim, cudaMemcpyHostToDevice, idx->stream);
+                if (e == cudaSuccess) e = cudaStreamSynchronize(idx->stream);
+                if (e != cudaSuccess) st = fail(LK_ECUDA, std::string("lk_index_load: ") + cudaGetErrorString(e));
+            }
+            if (st == 0 && h.len > 0) st = fill_device(idx, idx->d_cnorm, (size_t)h.len * 4, f, pin, hs);
+        }
+    }
+    if (st == 0 && fgetc(f) != EOF) st = fail(LK_EINVAL, "lk_index_load: the file is longer than its header says");
+    if (st == 0 && hs.h != h.checksum) st = fail(LK_EINVAL, "lk_index_load: checksum mismatch, the cache is damaged");
+    fclose(f);
+    pin.release();
+    if (st != 0) {
+        if (idx) lk_index_destroy(idx);
+        return st;
+    }
+    idx->len = h.len;
+    idx->center_live = h.center_live != 0;
+    idx->n_centered = h.n_centered;
+    idx->mu_n2 = h.mu_n2;
+    *out = idx;
     return LK_OK;
 }
 

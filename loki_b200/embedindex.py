@@ -13,6 +13,7 @@ runs on the GPU.  This module only marshals arguments.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Iterable, List, Optional, Sequence
 
@@ -38,6 +39,8 @@ def _sig(name, restype, *argtypes):
 
 _sig("lkx_new", _int, _int, _int, _int, C.POINTER(_vp))
 _sig("lkx_free", _int, _vp)
+_sig("lkx_save", _int, _vp, C.c_char_p, C.c_uint64)
+_sig("lkx_load", _int, C.c_char_p, C.c_uint64, _int, C.POINTER(_vp))
 _sig("lkx_add", _int, _vp, C.c_char_p, _vp, _int)
 _sig("lkx_add_batch", _int, _vp, _cpp, _vp, _i64, _int)
 _sig("lkx_delete", _int, _vp, C.c_char_p)
@@ -113,6 +116,20 @@ class VectorIndex:
         assert rows.ndim == 2 and rows.shape[0] == n
         arr = (C.c_char_p * max(n, 1))(*[p.encode("utf-8") for p in paths])
         check(lib.lkx_add_batch(self._h, arr, _lib.ptr(rows), n, rows.shape[1]))
+
+    def SaveCache(self, path: str, tag: int = 0) -> None:
+        """Write the built index and its paths (slot order) to `path` and `path`.paths."""
+        check(lib.lkx_save(self._h, os.fsencode(path), C.c_uint64(int(tag))))
+
+    @classmethod
+    def LoadCache(cls, path: str, tag: int = 0, device: int = 0) -> "VectorIndex":
+        """The index SaveCache wrote, without the row-by-row rebuild; raises when the tag
+        (model + row count), the sizes or the checksum do not match."""
+        h = _vp()
+        check(lib.lkx_load(os.fsencode(path), C.c_uint64(int(tag)), int(device), C.byref(h)))
+        self = cls.__new__(cls)
+        self._h = h
+        return self
 
     def Delete(self, path: str) -> None:
         check(lib.lkx_delete(self._h, path.encode("utf-8")))
