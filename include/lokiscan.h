@@ -283,6 +283,17 @@ LK_API int lk_seed_scores(const float *cands, int64_t n_cand, const float *seeds
                           float min_score, int64_t chunk, int device, int64_t *row_start, int32_t *out_seed,
                           float *out_score, int64_t cap, int64_t *out_total);
 
+/* ---- PCA projection for the embedding-space view ----------------------------- */
+
+/* Replaces embedvec.ProjectPCA3 (media-server/embedvec/pca.go:22-128): n vectors of dim floats
+ * (row-major) -> coords n x 3 float32, uniformly scaled into [-1, 1]^3, and the fraction of the
+ * total variance each component explains (zeros for components that do not exist).
+ *   workers   runtime.NumCPU() of the machine the reference would run on (its row chunks'
+ *             partial sums are merged in chunk order, pca.go:137-177): coords are bit-identical
+ *             to the reference's for that count.  The variance fractions agree to ~1e-13
+ *             relative (the reference sums the total variance as one long chain). */
+LK_API int lk_pca3(const float *vecs, int64_t n, int dim, int workers, int device, float *coords, double *variance);
+
 /* ---- statistics ----------------------------------------------------------- */
 
 typedef struct {

@@ -97,6 +97,7 @@ _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64,
 _sig("lk_stats", _int, _vp, C.POINTER(lk_stats_t))
 _sig("lk_index_set_batch_mode", _int, _vp, _int)
 _sig("lk_prescreen_pairs", _int, _vp, _i64, _int, C.c_float, _int, _vp, _vp, _vp)
+_sig("lk_pca3", _int, _vp, _i64, _int, _int, _int, _vp, _vp)
 _sig("lk_seed_scores", _int, _vp, _i64, _vp, _i64, _int, C.c_float, _i64, _int, _vp, _vp, _vp, _i64, _vp)
 _sig("lk_scan_i8_prealloc", _int, _int, _vp, _i64, _int, _i64, _vp, _vp, C.c_float, _int, _vp, _vp, _vp, _vp, _vp)
 LK_PREALLOC_MAX_K = 128
@@ -398,3 +399,14 @@ def seed_scores(cands, seeds, min_score: float, chunk: int = 0, device: int = 0)
         break
     n = int(total.value)
     return row_start, out_seed[:n].copy(), out_score[:n].copy()
+
+
+def pca3(vecs, workers: int = 1, device: int = 0):
+    """Three-component PCA projection: -> (coords[n, 3] float32 in [-1, 1], variance[3] float64)."""
+    v = np.ascontiguousarray(vecs, dtype=np.float32)
+    n = v.shape[0]
+    dim = v.shape[1] if v.ndim == 2 else 0
+    coords = np.zeros((max(n, 1), 3), np.float32)
+    variance = np.zeros(3, np.float64)
+    check(lib.lk_pca3(ptr(v) if n and dim else None, n, int(dim), int(workers), int(device), ptr(coords), ptr(variance)))
+    return coords[:n], variance

@@ -34,3 +34,20 @@ def decode_rows(blobs: Iterable[bytes], dim: int) -> np.ndarray:
         if len(b) == dim * 4:
             out[i] = np.frombuffer(b, dtype="<f4")
     return out
+
+
+def ProjectPCA3(vecs, workers: int | None = None, device: int = 0):
+    """media-server/embedvec/pca.go:22-128: -> (coords, variance): one [x, y, z] per input,
+    uniformly scaled into [-1, 1]^3, and the variance fraction of each component.
+
+    `workers` is the reference's runtime.NumCPU(): it fixes the order in which the reference
+    adds its per-chunk partial sums, and with it the last bits of the result (default: this
+    machine's CPU count, like the reference running here)."""
+    import os
+
+    from . import _lib
+    rows = [np.asarray(v, np.float32) for v in vecs]
+    if len(rows) == 0 or rows[0].size == 0:
+        return np.zeros((len(rows), 3), np.float32), np.zeros(3, np.float64)
+    x = np.stack(rows)
+    return _lib.pca3(x, workers if workers else (os.cpu_count() or 1), device)

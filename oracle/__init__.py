@@ -102,6 +102,8 @@ def lib():
     L.orc_seed_scores.restype = None
     L.orc_seed_scores_single.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, _f32p]
     L.orc_seed_scores_single.restype = None
+    L.orc_pca3.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _f32p, np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")]
+    L.orc_pca3.restype = None
     L.orc_dot32.argtypes = [_f32p, _f32p, C.c_int]
     L.orc_dot32.restype = C.c_float
     _lib = L
@@ -353,3 +355,18 @@ def seed_scores(cands, seeds, chunk: int = 0, grouped: bool = True) -> np.ndarra
 def dot32(a, b) -> np.float32:
     a, b = _f32(a), _f32(b)
     return np.float32(lib().orc_dot32(a, b, a.size))
+
+
+# ---- PCA projection (media-server/embedvec/pca.go:22-182) -----------------------------------
+
+def pca3(vecs, workers: int = 1):
+    """embedvec.ProjectPCA3 as it runs on a machine with `workers` CPUs:
+    -> (coords[n, 3] float32, variance[3] float64)."""
+    v = _f32(vecs)
+    n = v.shape[0]
+    d = v.shape[1] if v.ndim == 2 else 0
+    coords = np.zeros((max(n, 1), 3), np.float32)
+    variance = np.zeros(3, np.float64)
+    if n and d:
+        lib().orc_pca3(v, n, d, int(workers), coords.reshape(-1), variance)
+    return coords[:n], variance

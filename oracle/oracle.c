@@ -615,3 +615,126 @@ ORC_API void orc_prescreen_bruteforce(const float *v, int n, int d, float thresh
         count[i] = c;
     }
 }
+
+/* ------------------------------------------------------------------------- */
+/* embedvec/pca.go: three-component PCA projection                              */
+/* ------------------------------------------------------------------------- */
+
+static double pca_dot(const double *a, const double *b, int d) { /* pca.go:209-215 */
+    double s = 0;
+    for (int i = 0; i < d; i++) s += a[i] * b[i];
+    return s;
+}
+static void pca_orthogonalize(double *v, double *const *basis, int nb, int d) { /* pca.go:198-206 */
+    for (int b = 0; b < nb; b++) {
+        double p = pca_dot(v, basis[b], d);
+        for (int j = 0; j < d; j++) v[j] -= p * basis[b][j];
+    }
+}
+static double pca_normalize(double *v, int d) { /* pca.go:218-226 */
+    double n = sqrt(pca_dot(v, v, d));
+    if (n == 0) return 0;
+    for (int j = 0; j < d; j++) v[j] /= n;
+    return n;
+}
+/* u = Xc^T (Xc v) with on-the-fly centering; rows split into `workers` contiguous chunks whose
+ * partial sums are merged in chunk order (pca.go:130-182). */
+static void pca_cov_times(const float *x, int n, int d, const double *mean, const double *v, int workers, double *u) {
+    double mv = pca_dot(mean, v, d);
+    if (workers > n) workers = n;
+    int chunk = (n + workers - 1) / workers;
+    int nparts = (n + chunk - 1) / chunk;
+    double *pu = (double *)calloc((size_t)nparts * d, sizeof(double));
+    double *py = (double *)calloc((size_t)nparts, sizeof(double));
+    for (int w = 0, lo = 0; lo < n; w++, lo += chunk) {
+        int hi = lo + chunk < n ? lo + chunk : n;
+        double *uw = pu + (size_t)w * d;
+        double ysum = 0;
+        for (int i = lo; i < hi; i++) {
+            const float *row = x + (size_t)i * d;
+            double y = 0;
+            for (int j = 0; j < d; j++) y += (double)row[j] * v[j];
+            y -= mv;
+            ysum += y;
+            for (int j = 0; j < d; j++) uw[j] += y * (double)row[j];
+        }
+        py[w] = ysum;
+    }
+    double ysum = 0;
+    for (int j = 0; j < d; j++) u[j] = 0;
+    for (int w = 0; w < nparts; w++) {
+        ysum += py[w];
+        for (int j = 0; j < d; j++) u[j] += pu[(size_t)w * d + j];
+    }
+    for (int j = 0; j < d; j++) u[j] -= ysum * mean[j];
+    free(pu);
+    free(py);
+}
+
+/* ProjectPCA3 (pca.go:22-128).  coords is n x 3 float32, variance 3 doubles; `workers` stands
+ * for runtime.NumCPU() of the machine the reference runs on. */
+ORC_API void orc_pca3(const float *x, int n, int d, int workers, float *coords, double *variance) {
+    for (int i = 0; i < n * 3; i++) coords[i] = 0;
+    variance[0] = variance[1] = variance[2] = 0;
+    if (n == 0 || d == 0) return;
+    if (workers < 1) workers = 1;
+    double *mean = (double *)calloc((size_t)d, sizeof(double));
+    for (int i = 0; i < n; i++)
+        for (int j = 0; j < d; j++) mean[j] += (double)x[(size_t)i * d + j];
+    for (int j = 0; j < d; j++) mean[j] /= (double)n;
+    double total = 0;
+    for (int i = 0; i < n; i++)
+        for (int j = 0; j < d; j++) {
+            double dx = (double)x[(size_t)i * d + j] - mean[j];
+            total += dx * dx;
+        }
+    total /= (double)n;
+    if (total == 0) { free(mean); return; }
+    double *comps[3] = {0, 0, 0};
+    double eigen[3] = {0, 0, 0};
+    int nc = 0;
+    double *u = (double *)malloc(sizeof(double) * (size_t)d);
+    for (int c = 0; c < 3; c++) {
+        double *v = (double *)malloc(sizeof(double) * (size_t)d);
+        uint64_t state = 0x9E3779B97F4A7C15ull + (uint64_t)c * 0xBF58476D1CE4E5B9ull; /* pca.go:187-195 */
+        for (int j = 0; j < d; j++) {
+            state = state * 6364136223846793005ull + 1442695040888963407ull;
+            v[j] = (double)(int64_t)(state >> 11) / (double)(1ull << 52) - 1;
+        }
+        pca_orthogonalize(v, comps, nc, d);
+        if (pca_normalize(v, d) == 0) { free(v); break; }
+        double lambda = 0;
+        for (int iter = 0; iter < 100; iter++) {
+            pca_cov_times(x, n, d, mean, v, workers, u);
+            pca_orthogonalize(u, comps, nc, d);
+            lambda = pca_normalize(u, d);
+            if (lambda == 0) break;
+            int done = fabs(pca_dot(u, v, d)) > 1 - 1e-10;
+            memcpy(v, u, sizeof(double) * (size_t)d);
+            if (done) break;
+        }
+        if (lambda == 0) { free(v); break; }
+        comps[nc] = v;
+        eigen[nc] = lambda / (double)n;
+        nc++;
+    }
+    double mean_dot[3] = {0, 0, 0};
+    for (int c = 0; c < nc; c++) mean_dot[c] = pca_dot(mean, comps[c], d);
+    double max_abs = 0;
+    for (int i = 0; i < n; i++)
+        for (int c = 0; c < nc; c++) {
+            double sacc = 0;
+            for (int j = 0; j < d; j++) sacc += (double)x[(size_t)i * d + j] * comps[c][j];
+            sacc -= mean_dot[c];
+            coords[(size_t)i * 3 + c] = (float)sacc;
+            if (fabs(sacc) > max_abs) max_abs = fabs(sacc);
+        }
+    if (max_abs > 0) {
+        float sc = (float)(1 / max_abs);
+        for (int i = 0; i < n * 3; i++) coords[i] *= sc;
+    }
+    for (int c = 0; c < nc; c++) variance[c] = eigen[c] / total;
+    for (int c = 0; c < nc; c++) free(comps[c]);
+    free(u);
+    free(mean);
+}
