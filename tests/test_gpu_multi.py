@@ -97,3 +97,74 @@ def test_sharded_search_over_nccl_equals_single_index(lk, tmp_path):
                 assert np.array_equal(g[f"{mode}_{name}_scores"], scores), (mode, name)
                 assert np.array_equal(g[f"{mode}_{name}_iscores"], iscores), (mode, name)
             assert np.array_equal(g[f"big_{name}_ids"], big), name
+
+
+TIMEOUT_WORKER = r'''
+import os, sys, time
+sys.path.insert(0, os.environ["LK_ROOT"])
+import numpy as np
+import torch
+import torch.distributed as dist
+from loki_b200 import _lib as lk
+from tests.synth import gaussian_rows
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+uid = [lk.Comm.unique_id() if rank == 0 else None]
+dist.broadcast_object_list(uid, src=0)
+comm = lk.Comm(world, rank, rank, uid[0])
+handles = [None] * world
+dist.all_gather_object(handles, comm.peer_export())
+comm.peer_attach(handles)
+idx = lk.DeviceIndex(64, lk.LK_I8, device=rank)
+idx.append(gaussian_rows(5000, 64, 10 + rank))
+idx.attach_comm(comm, 5000 * rank)
+q = gaussian_rows(1, 64, 3)
+ids, _, _, counts = idx.search(q, 10)          # both ranks take part: a normal exchange
+assert counts[0] == 10
+dist.barrier()
+status = "no error"
+if rank == 0:
+    t0 = time.time()
+    try:                                        # rank 1 stays away: the wait inside the kernel must run out
+        idx.search(q, 10)
+    except lk.LokiError as e:
+        status = f"{e.status} after {time.time() - t0:.1f} s"
+else:
+    time.sleep(6.0)                             # between steps, nothing of this rank in flight
+with open(os.path.join(os.environ["LK_OUT"], f"timeout{rank}.txt"), "w") as f:
+    f.write(status)
+dist.barrier()
+idx.close()
+comm.close()
+dist.destroy_process_group()
+'''
+
+
+def test_a_rank_that_stays_away_ends_the_exchange_with_a_timeout(lk, tmp_path):
+    """The exchange inside the scan kernel waits for the other shards' lists with a 2-second
+    bound; when a rank does not take part the call returns LK_ETIMEOUT and the GPU stays usable."""
+    if lk.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    port = _free_port()
+    script = tmp_path / "timeout_worker.py"
+    script.write_text(TIMEOUT_WORKER)
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), LK_ROOT=ROOT, LK_OUT=str(tmp_path), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o[-3000:]
+    status = (tmp_path / "timeout0.txt").read_text()
+    assert status.startswith(f"{lk.LK_ETIMEOUT} after"), status
+    assert float(status.split()[2]) < 5.0
+    # the device that timed out still answers
+    idx = lk.DeviceIndex(64, lk.LK_I8)
+    from tests.synth import gaussian_rows
+    idx.append(gaussian_rows(1000, 64, 1))
+    assert idx.search(gaussian_rows(1, 64, 2), 5)[3][0] == 5
