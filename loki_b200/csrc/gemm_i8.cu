@@ -11,18 +11,21 @@
 //
 // Shape of one CTA (576 threads, one CTA per SM):
 //   warp 0     TMA producer: 2-D tiled loads (128-byte swizzle) of corpus tiles
-//              [128 rows x 128 K-bytes] into a ring of stages; loads the CTA's query
+//              [256 rows x 128 K-bytes] into a ring of stages; loads the CTA's query
 //              tile [128 queries x all K] once, it stays resident in shared memory
-//   warp 1     allocates tensor memory and issues the MMAs: D[128 rows x 128 queries]
-//              += A[128 x 32] * B[128 x 32]^T, four per 128-byte K slice; commits free
-//              the stage / publish the accumulator through mbarriers
-//   warps 2-17 epilogue: read the accumulator from tensor memory (one corpus row and 32
-//              queries per thread), test all 32 scores against the queries' running
-//              thresholds with one add and half an OR each, and append the few survivors to
-//              their queries' candidate lists; four accumulator buffers (all of tensor memory)
-//              let the following tiles' MMAs run meanwhile.  A list that fills up is cut back to its best k by a
-//              warp-wide selection (bisection on the score with the keys in registers), which
-//              also raises the query's threshold; lists are sorted once, at the end.
+//   warp 1     allocates tensor memory and issues the MMAs: D[128 queries x 256 rows]
+//              += Q[128 x 32] * R[256 x 32]^T, four per 128-byte K slice (the queries are the
+//              M side, so that every instruction carries N = 256: 128 x 256 x 32 per issue);
+//              commits free the stage / publish the accumulator through mbarriers.  Both
+//              single-thread roles run their loops warp-wide and let an elected lane issue.
+//   warps 2-17 epilogue: a tensor-memory lane is a query, a column a corpus row: a thread
+//              reads its query's scores of 64 rows per tile, tests them against the query's
+//              threshold (one register) with one add and half an OR each, and appends the few
+//              survivors to its query's candidate list; two accumulator buffers (all 512
+//              columns of tensor memory) let the next tile's MMAs run meanwhile.  A list that
+//              fills up is cut back to its best k by a warp-wide selection (bisection on the
+//              score with the keys in registers), which also raises the query's threshold;
+//              lists are sorted once, at the end.
 // A CTA owns one tile of 128 queries and every ns-th corpus tile; the CTAs of one query
 // tile split the corpus between them and their lists are merged by k_merge_lists.
 //
@@ -41,24 +44,21 @@
 
 namespace lk {
 
-constexpr int GM = 128;            // corpus rows per tile (MMA M, tensor-memory lanes)
-constexpr int GN = 128;            // queries per tile (MMA N, tensor-memory columns)
+constexpr int GN = 128;            // queries per tile (MMA M, tensor-memory lanes)
+constexpr int GM = 256;            // corpus rows per tile (MMA N, tensor-memory columns)
 constexpr int GSLICE = 128;        // K bytes per shared-memory slice: one swizzle row
-constexpr int GSLICE_BYTES = GM * GSLICE;  // 16 KB: one slice of a 128-row tile
+constexpr int GQ_SLICE_BYTES = GN * GSLICE;  // 16 KB: one K slice of the 128-query tile
+constexpr int GSLICE_BYTES = GM * GSLICE;    // 32 KB: one K slice of a 256-row corpus tile
 constexpr int GCAP_MAX = 1024;     // most candidate keys a query holds between prunes (k <= 256)
 constexpr int GEPI_WARPS = 16;     // epilogue warps: four per tensor-memory lane quadrant, 32 queries each
 constexpr int GEPI_THREADS = GEPI_WARPS * 32;
 constexpr int GTHREADS = 64 + GEPI_THREADS;
-constexpr int GACC = 4;            // accumulators in tensor memory: 4 x 128 columns = all 512
-// A query's list holds cap = pow2ceil(2k + 256) keys.  One tile adds at most 128; the check
-// that triggers a prune may miss what other warps append while it runs, so it leaves room
-// for two tiles: a list is cut back to k whenever it exceeds cap - 256, i.e. after at least
-// k new survivors.  Small lists keep the selections short and the thresholds fresh.
-__host__ __device__ inline int gemm_cap(int k) {
-    int c = 512;
-    while (c < 2 * k + 2 * GM) c <<= 1;
-    return c;
-}
+constexpr int GACC = 2;            // accumulators in tensor memory: 2 x 256 columns = all 512
+// A query's list holds GCAP_MAX keys.  One tile adds at most 256 to a list; the check that
+// triggers a cut may miss what other warps append while it runs, so it leaves room for two
+// tiles: a list is cut back to k whenever it exceeds cap - 512, i.e. after at least
+// 512 - k new survivors.
+__host__ __device__ inline int gemm_cap(int) { return GCAP_MAX; }
 constexpr long long GWAIT_CLOCKS = 4000000000ll;  // ~2 s at 2 GHz
 
 __device__ __forceinline__ unsigned g_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -103,6 +103,23 @@ __device__ __forceinline__ bool g_mbar_wait(unsigned long long *bar, unsigned pa
         }
     }
 }
+// The whole (converged) warp waits for a phase, but only lane 0 polls the barrier: 18 warps of
+// pollers would compete with the MMAs' operand reads for shared memory.
+__device__ __forceinline__ bool g_mbar_wait_warp(unsigned long long *bar, unsigned parity, volatile int *cta_failed) {
+    int ok = 0;
+    if ((threadIdx.x & 31) == 0) ok = g_mbar_wait(bar, parity, cta_failed) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// One lane of the (converged) warp: the issuer of a single-thread instruction.
+__device__ __forceinline__ bool g_elect_one() {
+    unsigned pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 // 2-D tiled TMA load: box at (x = byte column, y = row) of the tensor map -> shared memory
 __device__ __forceinline__ void g_tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, unsigned long long *bar) {
     asm volatile(
@@ -121,8 +138,8 @@ __device__ __forceinline__ unsigned long long g_smem_desc(unsigned addr) {
     d |= (unsigned long long)2 << 61;                          // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: int8 x int8 (both signed, K-major) -> int32, M = 128, N = 128.
-constexpr unsigned G_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(GN >> 3) << 17) | ((unsigned)(GM >> 4) << 24);
+// Instruction descriptor: int8 x int8 (both signed, K-major) -> int32, M = 128 queries, N = 256 rows.
+constexpr unsigned G_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(GM >> 3) << 17) | ((unsigned)(GN >> 4) << 24);
 
 __device__ __forceinline__ void g_mma_i8(unsigned tmem_d, unsigned long long da, unsigned long long db, bool accumulate) {
     const unsigned acc = accumulate ? 1u : 0u;
@@ -295,9 +312,8 @@ __device__ inline void g_select_query(GemmShared *ctl, unsigned long long *cand_
     __syncwarp();
 }
 
-__device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q, int q, int k, int cap, int lane) {
-    if (cap <= 512) g_select_query<16>(ctl, cand_q, q, k, lane);
-    else g_select_query<GCAP_MAX / 32>(ctl, cand_q, q, k, lane);
+__device__ inline void g_prune_query(GemmShared *ctl, unsigned long long *cand_q, int q, int k, int, int lane) {
+    g_select_query<GCAP_MAX / 32>(ctl, cand_q, q, k, lane);
 }
 
 __global__ void __launch_bounds__(GTHREADS, 1)
@@ -306,8 +322,8 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     extern __shared__ unsigned char g_raw[];
     // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address
     unsigned char *smem = g_raw + ((1024u - (g_smem(g_raw) & 1023u)) & 1023u);
-    unsigned char *sm_b = smem;                                        // [ks][128 queries][128 B]
-    unsigned char *sm_a = sm_b + (size_t)a.ks * GSLICE_BYTES;          // [stages][128 rows][128 B]
+    unsigned char *sm_b = smem;                                        // [ks][128 queries][128 B]: the MMA's A operand
+    unsigned char *sm_a = sm_b + (size_t)a.ks * GQ_SLICE_BYTES;        // [stages][256 rows][128 B]: the MMA's B operand
     const int cap = gemm_cap(a.k), limit = cap - 2 * GM;
     GemmShared *ctl = reinterpret_cast<GemmShared *>(sm_a + (size_t)a.stages * GSLICE_BYTES);
 
@@ -338,10 +354,10 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
         ctl->thr_score[tid] = live ? -(1 << 30) : (1 << 30);  // every real score is far inside +-2^30
         ctl->cnt[tid] = 0;
     }
-    if (warp == 1) {  // tensor memory: GACC accumulators x 128 columns
+    if (warp == 1) {  // tensor memory: GACC accumulators x 256 columns
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(g_smem(&ctl->tmem_base)),
-                     "r"(GACC * GN)
+                     "r"(GACC * GM)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -351,117 +367,123 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     const unsigned tmem_base = ctl->tmem_base;
     volatile int *failed = &ctl->failed;
 
+    // The two single-thread roles run their loops with the whole warp (uniform control flow,
+    // warp-uniform values: loop state and descriptors can live in uniform registers, which the
+    // TMA and MMA instructions take their operands from) and let one elected lane issue.
+    // With the loops inside `if (lane == 0)` every MMA cost about 155 clocks to issue, more than
+    // twice what the tensor pipe needs to execute it.
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            g_mbar_expect_tx(&ctl->b_full, (unsigned)(a.ks * GSLICE_BYTES));
+        if (g_elect_one()) {
+            g_mbar_expect_tx(&ctl->b_full, (unsigned)(a.ks * GQ_SLICE_BYTES));
             for (int s = 0; s < a.ks; ++s)
-                g_tma_load_2d(sm_b + (size_t)s * GSLICE_BYTES, &tm_queries, s * GSLICE, q0, &ctl->b_full);
-            int stage = 0;
-            unsigned phase = 0;
-            for (long long t = slice; t < n_tiles && !*failed; t += nslices) {
-                for (int s = 0; s < a.ks; ++s) {
-                    { GPROF_T0; const bool w = g_mbar_wait(&ctl->empty[stage], phase ^ 1u, failed); GPROF_ADD(0); if (!w) break; }
+                g_tma_load_2d(sm_b + (size_t)s * GQ_SLICE_BYTES, &tm_queries, s * GSLICE, q0, &ctl->b_full);
+        }
+        __syncwarp();
+        int stage = 0;
+        unsigned phase = 0;
+        bool ok = true;
+        for (long long t = slice; ok && t < n_tiles; t += nslices) {
+            for (int s = 0; s < a.ks; ++s) {
+                { GPROF_T0; ok = g_mbar_wait_warp(&ctl->empty[stage], phase ^ 1u, failed); if (lane == 0) GPROF_ADD(0); }
+                if (!ok) break;
+                if (g_elect_one()) {
                     g_mbar_expect_tx(&ctl->full[stage], (unsigned)GSLICE_BYTES);
                     g_tma_load_2d(sm_a + (size_t)stage * GSLICE_BYTES, &tm_rows, s * GSLICE, (int)(t * GM),
                                   &ctl->full[stage]);
-                    if (++stage == a.stages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                }
+                __syncwarp();
+                if (++stage == a.stages) {
+                    stage = 0;
+                    phase ^= 1u;
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            bool ok = g_mbar_wait(&ctl->b_full, 0u, failed);
-            const unsigned long long da0 = g_smem_desc(g_smem(sm_a)), db0 = g_smem_desc(g_smem(sm_b));
-            int stage = 0, acc = 0;
-            unsigned phase = 0, acc_phase = 0;
-            for (long long t = slice; ok && t < n_tiles; t += nslices) {
-                { GPROF_T0; ok = g_mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, failed); GPROF_ADD(1); }
+        bool ok = g_mbar_wait_warp(&ctl->b_full, 0u, failed);
+        const unsigned long long da0 = g_smem_desc(g_smem(sm_a)), db0 = g_smem_desc(g_smem(sm_b));
+        int stage = 0, acc = 0;
+        unsigned phase = 0, acc_phase = 0;
+        for (long long t = slice; ok && t < n_tiles; t += nslices) {
+            { GPROF_T0; ok = g_mbar_wait_warp(&ctl->tmem_empty[acc], acc_phase ^ 1u, failed); if (lane == 0) GPROF_ADD(1); }
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned d = tmem_base + (unsigned)(acc * GM);
+            for (int s = 0; s < a.ks; ++s) {
+                { GPROF_T0; ok = g_mbar_wait_warp(&ctl->full[stage], phase, failed); if (lane == 0) GPROF_ADD(2); }
                 if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned d = tmem_base + (unsigned)(acc * GN);
-                for (int s = 0; s < a.ks && ok; ++s) {
-                    { GPROF_T0; ok = g_mbar_wait(&ctl->full[stage], phase, failed); GPROF_ADD(2); }
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // the start-address field counts 16-byte units: one slice further = + 1024
-                    const unsigned long long da = da0 + (unsigned long long)(stage * (GSLICE_BYTES >> 4));
-                    const unsigned long long db = db0 + (unsigned long long)(s * (GSLICE_BYTES >> 4));
+                // (no tcgen05 fence here: the stage was filled by TMA, whose completion on the mbarrier
+                // orders it for the MMAs; a fence per slice drained the MMA queue at every slice)
+                // the start-address field counts 16-byte units: one slice further = + 1024
+                const unsigned long long da = da0 + (unsigned long long)(stage * (GSLICE_BYTES >> 4));     // corpus rows
+                const unsigned long long db = db0 + (unsigned long long)(s * (GQ_SLICE_BYTES >> 4));      // queries
+                if (g_elect_one()) {
 #pragma unroll
                     for (int k4 = 0; k4 < GSLICE / 32; ++k4)  // 32 K-bytes per MMA: +2 in 16-byte units
-                        g_mma_i8(d, da + (unsigned long long)(2 * k4), db + (unsigned long long)(2 * k4), (s | k4) != 0);
+                        g_mma_i8(d, db + (unsigned long long)(2 * k4), da + (unsigned long long)(2 * k4), (s | k4) != 0);
                     g_mma_commit(&ctl->empty[stage]);  // the stage is free once these MMAs have read it
-                    if (++stage == a.stages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
                 }
-                if (!ok) break;
-                g_mma_commit(&ctl->tmem_full[acc]);  // accumulator complete
-                if (++acc == GACC) {
-                    acc = 0;
-                    acc_phase ^= 1u;
+                __syncwarp();
+                if (++stage == a.stages) {
+                    stage = 0;
+                    phase ^= 1u;
                 }
+            }
+            if (!ok) break;
+            if (g_elect_one()) g_mma_commit(&ctl->tmem_full[acc]);  // accumulator complete
+            __syncwarp();
+            if (++acc == GACC) {
+                acc = 0;
+                acc_phase ^= 1u;
             }
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        // 16 warps: a warp may read the tensor-memory lanes 32 * (warp % 4) .. + 31 (the hardware's
-        // rule), i.e. 32 corpus rows, and takes one quarter of the 128 query columns: one corpus
-        // row x 32 queries per thread and tile.
+        // 16 warps.  A tensor-memory lane is a query, a column a corpus row of the tile.  A warp may
+        // read the lanes 32 * (warp % 4) .. + 31 (the hardware's rule), i.e. 32 queries, and takes
+        // one quarter of the 256 columns: one query x 64 corpus rows per thread and tile, so the
+        // threshold is one register and every survivor of a thread goes to the thread's own query.
         const int ew = warp - 2;       // 0..15
         const int quad = warp & 3;
-        const int c0 = (ew >> 2) * 32;
+        const int c0 = (ew >> 2) * 64;
         const int etid = ew * 32 + lane;
+        const int q = quad * 32 + lane;  // this thread's query within the tile
         unsigned long long *cand = a.cand + (size_t)blockIdx.x * GN * GCAP_MAX;
+        unsigned long long *my_list = cand + (size_t)q * GCAP_MAX;
         int acc = 0;
         unsigned acc_phase = 0;
         bool ok = true;
         for (long long t = slice; t < n_tiles; t += nslices) {
             bool have;
-            { GPROF_T0; have = g_mbar_wait(&ctl->tmem_full[acc], acc_phase, failed); if (etid == 0) GPROF_ADD(3); }
+            { GPROF_T0; have = g_mbar_wait_warp(&ctl->tmem_full[acc], acc_phase, failed); if (etid == 0) GPROF_ADD(3); }
             GPROF_T0;
             if (!have) ctl->epilogue_failed = 1;  // read by all epilogue threads behind the barrier below
             if (have) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const long long row = t * GM + quad * 32 + lane;
-                int v[32];
-                g_tmem_ld32(tmem_base + (unsigned)(acc * GN + c0) + ((unsigned)(quad * 32) << 16), v);
-                // the 32 score thresholds of these queries, while the load is in flight
-                int ts[32];
+                const int ts = ctl->thr_score[q];
+                const long long row0 = t * GM + c0;
+                const int rows_here = (int)min((long long)64, a.n - row0);  // columns past the corpus hold zeros
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    int v[32];
+                    g_tmem_ld32(tmem_base + (unsigned)(acc * GM + c0 + h * 32) + ((unsigned)(quad * 32) << 16), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    // first test, branch-free: ts - v - 1 is negative exactly when v >= ts (both are far
+                    // from the ends of the int range), so the sign of the OR says "some row passes"
+                    int any = 0;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const int4 w = *reinterpret_cast<const int4 *>(&ctl->thr_score[c0 + j]);
-                    ts[j] = w.x; ts[j + 1] = w.y; ts[j + 2] = w.z; ts[j + 3] = w.w;
-                }
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                // first test, branch-free: ts - v - 1 is negative exactly when v >= ts (both are far
-                // from the ends of the int range), so the sign of the OR says "some query accepts"
-                int any = 0;
+                    for (int j = 0; j < 32; ++j) any |= ts - v[j] - 1;
+                    if (any < 0) {  // rare once the threshold has risen
+                        const unsigned long long thr = ctl->thr[q];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) any |= ts[j] - v[j] - 1;
-                const bool mine = any < 0 && row < a.n;
-                if (__any_sync(0xffffffffu, mine)) {  // some lane has a survivor: rare once the thresholds have risen
-                    // column by column, the whole warp: the lanes that pass column j all append to
-                    // the same query, so one atomic reserves their places
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const bool p = mine && v[j] >= ts[j];
-                        const unsigned m = __ballot_sync(0xffffffffu, p);
-                        if (m != 0u) {
-                            const int q = c0 + j;
-                            const unsigned long long key = make_key(ord_from_i32(v[j]), (unsigned)row);
-                            const unsigned m2 = __ballot_sync(0xffffffffu, p && key > ctl->thr[q]);
-                            if (m2 != 0u) {
-                                int base = 0;
-                                if (lane == __ffs(m2) - 1) base = atomicAdd(&ctl->cnt[q], __popc(m2));
-                                base = __shfl_sync(0xffffffffu, base, __ffs(m2) - 1);
-                                const int pos = base + __popc(m2 & lanemask_lt());
-                                if (((m2 >> lane) & 1u) && pos < cap) __stcg(cand + (size_t)q * GCAP_MAX + pos, key);
+                        for (int j = 0; j < 32; ++j) {
+                            if (v[j] >= ts && h * 32 + j < rows_here) {
+                                const unsigned long long key = make_key(ord_from_i32(v[j]), (unsigned)(row0 + h * 32 + j));
+                                if (key > thr) {
+                                    const int pos = atomicAdd(&ctl->cnt[q], 1);
+                                    if (pos < cap) __stcg(my_list + pos, key);
+                                }
                             }
                         }
                     }
@@ -530,7 +552,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
     if (tid == 0 && ctl->failed != 0 && a.error != nullptr) atomicExch(a.error, 1);
     if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GACC * GN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GACC * GM) : "memory");
     }
 }
 
@@ -558,14 +580,14 @@ static encode_fn get_encode() {
     return fn;
 }
 
-// [rows x ld bytes] row-major int8 matrix, boxes of 128 rows x 128 bytes, 128-byte swizzle;
+// [rows x ld bytes] row-major int8 matrix, boxes of box_rows rows x 128 bytes, 128-byte swizzle;
 // out-of-range rows and columns read as zero.
-static int make_map(CUtensorMap *tm, const void *base, long long rows, long long ld) {
+static int make_map(CUtensorMap *tm, const void *base, long long rows, long long ld, int box_rows) {
     encode_fn enc = get_encode();
     if (!enc) return fail(LK_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)std::max<long long>(rows, 1)};
     const cuuint64_t strides[1] = {(cuuint64_t)ld};
-    const cuuint32_t box[2] = {(cuuint32_t)GSLICE, (cuuint32_t)GM};
+    const cuuint32_t box[2] = {(cuuint32_t)GSLICE, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -584,7 +606,7 @@ extern "C" __attribute__((visibility("default"))) void lk_debug_gemm_profile(uns
 }
 #endif
 
-bool gemm_supported(long long ld, int k) { return ld % 16 == 0 && ld <= 1536 && k >= 1 && k <= GEMM_MAX_K; }
+bool gemm_supported(long long ld, int k) { return ld % 16 == 0 && ld <= 1152 && k >= 1 && k <= GEMM_MAX_K; }
 
 size_t gemm_cand_bytes(int grid) { return (size_t)grid * GN * GCAP_MAX * 8; }
 
@@ -599,11 +621,11 @@ int gemm_launch(const unsigned char *d_rows, long long n, long long ld, const un
                 unsigned long long *d_cand, unsigned long long *d_lists, int *d_error, int sm_count,
                 cudaStream_t stream, long long *launches) {
     CUtensorMap tm_rows, tm_q;
-    LK_TRY(make_map(&tm_rows, d_rows, n, ld));
-    LK_TRY(make_map(&tm_q, d_queries, nq, ld));
+    LK_TRY(make_map(&tm_rows, d_rows, n, ld, GM));
+    LK_TRY(make_map(&tm_q, d_queries, nq, ld, GN));
     const int ks = (int)((ld + GSLICE - 1) / GSLICE);
-    const size_t fixed = (size_t)ks * GSLICE_BYTES + sizeof(GemmShared) + 1024;
-    int stages = (int)((220 * 1024 - fixed) / GSLICE_BYTES);
+    const size_t fixed = (size_t)ks * GQ_SLICE_BYTES + sizeof(GemmShared) + 1024;
+    int stages = (int)((224 * 1024 - fixed) / GSLICE_BYTES);
     stages = std::min(stages, 8);
     if (stages < 2) return fail(LK_ERANGE, "gemm search: rows too wide for the resident query tile");
     const size_t smem = fixed + (size_t)stages * GSLICE_BYTES;
