@@ -968,43 +968,89 @@ struct CacheHeader {  // 128 bytes, little-endian like the machine
 };
 static_assert(sizeof(CacheHeader) == 128, "cache header layout");
 
-// word-wise FNV-1a-style hash: fast enough for gigabytes, sensitive to any flipped bit
+// Word-wise FNV-1a-style hash over four interleaved lanes (the multiply's latency would
+// otherwise cap one lane near 4 GB/s); sensitive to any flipped bit.  Chunks are multiples of
+// 32 bytes except the last one of a region, whose tail goes through lane 0 byte by byte.
 struct Hasher {
-    uint64_t h = 0xcbf29ce484222325ull;
+    uint64_t lane[4] = {0xcbf29ce484222325ull, 0x84222325cbf29ce4ull, 0x9ce484222325cbf2ull, 0x2325cbf29ce48422ull};
     void add(const void *p, size_t n) {
         const unsigned char *b = (const unsigned char *)p;
         size_t i = 0;
-        for (; i + 8 <= n; i += 8) {
-            uint64_t w;
-            memcpy(&w, b + i, 8);
-            h = (h ^ w) * 0x100000001b3ull;
-            h ^= h >> 29;
+        uint64_t h0 = lane[0], h1 = lane[1], h2 = lane[2], h3 = lane[3];
+        for (; i + 32 <= n; i += 32) {
+            uint64_t w[4];
+            memcpy(w, b + i, 32);
+            h0 = (h0 ^ w[0]) * 0x100000001b3ull; h0 ^= h0 >> 29;
+            h1 = (h1 ^ w[1]) * 0x100000001b3ull; h1 ^= h1 >> 29;
+            h2 = (h2 ^ w[2]) * 0x100000001b3ull; h2 ^= h2 >> 29;
+            h3 = (h3 ^ w[3]) * 0x100000001b3ull; h3 ^= h3 >> 29;
         }
-        for (; i < n; ++i) h = (h ^ b[i]) * 0x100000001b3ull;
+        for (; i < n; ++i) h0 = (h0 ^ b[i]) * 0x100000001b3ull;
+        lane[0] = h0; lane[1] = h1; lane[2] = h2; lane[3] = h3;
+    }
+    uint64_t value() const {
+        uint64_t h = lane[0];
+        for (int i = 1; i < 4; ++i) h = (h ^ lane[i]) * 0x100000001b3ull;
+        return h;
     }
 };
 
 constexpr size_t kCacheChunk = 32u << 20;
 
-// device -> file (through pinned memory), hashing on the way
-int dump_device(lk_index *idx, const void *d, size_t bytes, FILE *f, lk::PinnedBuf &pin, Hasher &hs) {
-    for (size_t off = 0; off < bytes; off += kCacheChunk) {
-        const size_t m = std::min(kCacheChunk, bytes - off);
-        LK_CUDA(cudaMemcpyAsync(pin.p, (const unsigned char *)d + off, m, cudaMemcpyDeviceToHost, idx->stream));
-        LK_CUDA(cudaStreamSynchronize(idx->stream));
-        hs.add(pin.p, m);
-        if (fwrite(pin.p, 1, m, f) != m) return fail(LK_EINVAL, "lk_index_save: write failed");
+// Two pinned buffers with an event each, so that the copy of one chunk overlaps the file
+// I/O and hashing of the other.
+struct CachePipe {
+    lk::PinnedBuf buf[2];
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    int init() {
+        for (int i = 0; i < 2; ++i) {
+            LK_TRY(buf[i].reserve(kCacheChunk));
+            LK_CUDA(cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming));
+        }
+        return 0;
+    }
+    ~CachePipe() {
+        for (int i = 0; i < 2; ++i) {
+            buf[i].release();
+            if (ev[i]) cudaEventDestroy(ev[i]);
+        }
+    }
+};
+
+// device -> file, hashing on the way: chunk i is written while chunk i + 1 is copied
+int dump_device(lk_index *idx, const void *d, size_t bytes, FILE *f, CachePipe &pp, Hasher &hs) {
+    const size_t n_chunks = (bytes + kCacheChunk - 1) / kCacheChunk;
+    auto start = [&](size_t c) -> int {
+        const size_t off = c * kCacheChunk, m = std::min(kCacheChunk, bytes - off);
+        LK_CUDA(cudaMemcpyAsync(pp.buf[c & 1].p, (const unsigned char *)d + off, m, cudaMemcpyDeviceToHost, idx->stream));
+        LK_CUDA(cudaEventRecord(pp.ev[c & 1], idx->stream));
+        return 0;
+    };
+    if (n_chunks > 0) LK_TRY(start(0));
+    for (size_t c = 0; c < n_chunks; ++c) {
+        if (c + 1 < n_chunks) LK_TRY(start(c + 1));
+        LK_CUDA(cudaEventSynchronize(pp.ev[c & 1]));
+        const size_t m = std::min(kCacheChunk, bytes - c * kCacheChunk);
+        hs.add(pp.buf[c & 1].p, m);
+        if (fwrite(pp.buf[c & 1].p, 1, m, f) != m) return fail(LK_EINVAL, "lk_index_save: write failed");
     }
     return 0;
 }
-int fill_device(lk_index *idx, void *d, size_t bytes, FILE *f, lk::PinnedBuf &pin, Hasher &hs) {
-    for (size_t off = 0; off < bytes; off += kCacheChunk) {
-        const size_t m = std::min(kCacheChunk, bytes - off);
-        if (fread(pin.p, 1, m, f) != m) return fail(LK_EINVAL, "lk_index_load: the file is shorter than its header says");
-        hs.add(pin.p, m);
-        LK_CUDA(cudaMemcpyAsync((unsigned char *)d + off, pin.p, m, cudaMemcpyHostToDevice, idx->stream));
-        LK_CUDA(cudaStreamSynchronize(idx->stream));
+// file -> device: chunk i is uploaded while chunk i + 1 is read and hashed
+int fill_device(lk_index *idx, void *d, size_t bytes, FILE *f, CachePipe &pp, Hasher &hs) {
+    const size_t n_chunks = (bytes + kCacheChunk - 1) / kCacheChunk;
+    bool used[2] = {false, false};
+    for (size_t c = 0; c < n_chunks; ++c) {
+        const int b = (int)(c & 1);
+        if (used[b]) LK_CUDA(cudaEventSynchronize(pp.ev[b]));  // its previous upload has left the buffer
+        const size_t off = c * kCacheChunk, m = std::min(kCacheChunk, bytes - off);
+        if (fread(pp.buf[b].p, 1, m, f) != m) return fail(LK_EINVAL, "lk_index_load: the file is shorter than its header says");
+        hs.add(pp.buf[b].p, m);
+        LK_CUDA(cudaMemcpyAsync((unsigned char *)d + off, pp.buf[b].p, m, cudaMemcpyHostToDevice, idx->stream));
+        LK_CUDA(cudaEventRecord(pp.ev[b], idx->stream));
+        used[b] = true;
     }
+    LK_CUDA(cudaStreamSynchronize(idx->stream));
     return 0;
 }
 
@@ -1020,8 +1066,8 @@ int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
     const std::string tmp = std::string(path) + ".tmp";
     FILE *f = fopen(tmp.c_str(), "wb");
     if (!f) return fail(LK_EINVAL, std::string("lk_index_save: cannot create ") + tmp);
-    lk::PinnedBuf pin;
-    int st = pin.reserve(kCacheChunk);
+    CachePipe pin;
+    int st = pin.init();
     CacheHeader h;
     memset(&h, 0, sizeof(h));
     memcpy(h.magic, "LKIDX001", 8);
@@ -1048,11 +1094,10 @@ int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
         }
     }
     if (st == 0) {
-        h.checksum = hs.h;
+        h.checksum = hs.value();
         if (fseek(f, 0, SEEK_SET) != 0 || fwrite(&h, 1, sizeof(h), f) != sizeof(h)) st = fail(LK_EINVAL, "lk_index_save: write failed");
     }
     if (fclose(f) != 0 && st == 0) st = fail(LK_EINVAL, "lk_index_save: close failed");
-    pin.release();
     if (st == 0 && rename(tmp.c_str(), path) != 0) st = fail(LK_EINVAL, std::string("lk_index_save: cannot rename to ") + path);
     if (st != 0) remove(tmp.c_str());
     return st;
@@ -1074,8 +1119,8 @@ int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out) {
     lk_index *idx = nullptr;
     if (st == 0) st = lk_index_create(h.dim, h.store, h.centered, device, &idx);
     if (st == 0 && idx->ld != h.ld) st = fail(LK_EINVAL, "lk_index_load: row stride of the cache does not match this library");
-    lk::PinnedBuf pin;
-    if (st == 0) st = pin.reserve(kCacheChunk);
+    CachePipe pin;
+    if (st == 0) st = pin.init();
     Hasher hs;
     if (st == 0 && h.len > 0) {
         st = grow_rows(idx, h.len);
@@ -1098,9 +1143,8 @@ int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out) {
         }
     }
     if (st == 0 && fgetc(f) != EOF) st = fail(LK_EINVAL, "lk_index_load: the file is longer than its header says");
-    if (st == 0 && hs.h != h.checksum) st = fail(LK_EINVAL, "lk_index_load: checksum mismatch, the cache is damaged");
+    if (st == 0 && hs.value() != h.checksum) st = fail(LK_EINVAL, "lk_index_load: checksum mismatch, the cache is damaged");
     fclose(f);
-    pin.release();
     if (st != 0) {
         if (idx) lk_index_destroy(idx);
         return st;
