@@ -211,10 +211,18 @@ LK_API int lk_index_set_shard_base(lk_index *idx, int64_t shard_base);
 
 /* All pairs i<j of hashes[0..n) with popcount(a^b) <= radius, written to `pairs`
  * as (i,j) uint32 couples in lexicographic order, at most cap couples;
- * *count = total found (may exceed cap).  part/parts split the upper triangle
- * across callers (0/1 = everything). */
+ * *count = total found (may exceed cap; which cap pairs are kept is then unspecified).
+ * part/parts split the work across callers (0/1 = everything): the shares are disjoint and
+ * their union is the complete result for any parts. */
 LK_API int lk_hamming_pairs(const uint64_t *hashes, int64_t n, int radius, int part, int parts,
                             int device, uint32_t *pairs, int64_t cap, int64_t *count);
+/* The same search spread over the GPUs of a communicator (every rank passes the same hashes:
+ * 2,000,000 of them are 16 MB): rank r tests share r of world, the per-GPU pair lists are
+ * all-gathered (NCCL: counts, then lists padded to the longest) and sorted on every GPU, and
+ * every rank receives the complete ordered list.  Structure of the reference's tiled all-pairs
+ * sweep with per-worker lists merged in order (media-server/tasks/face_cluster.go:1189-1285). */
+LK_API int lk_hamming_pairs_sharded(lk_comm *c, const uint64_t *hashes, int64_t n, int radius,
+                                    uint32_t *pairs, int64_t cap, int64_t *count);
 /* One hash against n: ids (ascending) and distances of those within radius. */
 LK_API int lk_hamming_scan(const uint64_t *hashes, int64_t n, uint64_t query, int radius,
                            int device, uint32_t *out_ids, int32_t *out_dist, int64_t cap,

@@ -93,6 +93,7 @@ _sig("lk_comm_peer_attach", _int, _vp, _vp)
 _sig("lk_index_attach_comm", _int, _vp, _vp, _i64)
 _sig("lk_index_set_shard_base", _int, _vp, _i64)
 _sig("lk_hamming_pairs", _int, _vp, _i64, _int, _int, _int, _int, _vp, _i64, C.POINTER(_i64))
+_sig("lk_hamming_pairs_sharded", _int, _vp, _vp, _i64, _int, _vp, _i64, C.POINTER(_i64))
 _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64, C.POINTER(_i64))
 _sig("lk_stats", _int, _vp, C.POINTER(lk_stats_t))
 _sig("lk_index_set_batch_mode", _int, _vp, _int)
@@ -338,6 +339,15 @@ class Comm:
         blob = b"".join(bytes(h) for h in handles)
         assert len(blob) == 64 * self.world
         check(lib.lk_comm_peer_attach(self._h, C.create_string_buffer(blob, len(blob))))
+
+    def hamming_pairs(self, hashes, radius: int, cap: int = 1 << 22):
+        """All pairs within `radius`, the search split over the ranks (every rank passes the same
+        hashes and receives the complete sorted list): -> (pairs[m, 2] uint32, total)."""
+        h = np.ascontiguousarray(hashes, dtype=np.uint64)
+        pairs = np.empty((max(cap, 1), 2), np.uint32)
+        cnt = _i64(0)
+        check(lib.lk_hamming_pairs_sharded(self._h, ptr(h), h.size, int(radius), ptr(pairs), int(cap), C.byref(cnt)))
+        return pairs[:min(cnt.value, cap)].copy(), int(cnt.value)
 
     def close(self):
         if getattr(self, "_h", None):

@@ -207,6 +207,22 @@ int lk_comm_peer_attach(lk_comm *c, const void *handles) {
     return LK_OK;
 }
 
+int lk_hamming_pairs_sharded(lk_comm *c, const uint64_t *hashes, int64_t n, int radius, uint32_t *pairs, int64_t cap,
+                             int64_t *count) {
+    if (!c || n < 0 || (n > 0 && !hashes) || radius < 0 || radius > 64 || cap < 0 || (cap > 0 && !pairs) || !count)
+        return fail(LK_EINVAL, "lk_hamming_pairs_sharded: bad argument");
+    if (n > 0xffffffffll) return fail(LK_ERANGE, "lk_hamming_pairs_sharded: more than 2^32 hashes");
+    *count = 0;
+    if (n < 2) return LK_OK;
+    NcclApi *api = nccl_api();
+    if (!api) return nccl_unavailable();
+    const HamAllGather gather = [api, c](const void *send, void *recv, size_t bytes, cudaStream_t st) -> int {
+        LK_NCCL(api, api->AllGather(send, recv, bytes, ncclUint8, c->comm, st));
+        return LK_OK;
+    };
+    return ham_pairs(hashes, n, radius, c->rank, c->world, c->device, pairs, cap, count, &gather);
+}
+
 int lk_comm_destroy(lk_comm *c) {
     if (!c) return LK_OK;
     NcclApi *api = nccl_api();

@@ -90,6 +90,8 @@ def lib():
     L.orc_topk_f32.restype = C.c_int
     L.orc_hamming_pairs.argtypes = [_u64p, C.c_int64, C.c_int, _u32p, C.c_int64]
     L.orc_hamming_pairs.restype = C.c_int64
+    L.orc_hamming_pairs_rows.argtypes = [_u64p, C.c_int64, C.c_int, C.c_int64, C.c_int64, _u32p, C.c_int64]
+    L.orc_hamming_pairs_rows.restype = C.c_int64
     L.orc_hamming_scan.argtypes = [_u64p, C.c_int64, C.c_uint64, _i32p]
     L.orc_hamming_scan.restype = None
     _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
@@ -241,6 +243,32 @@ def hamming_pairs(h, radius, cap=None):
     pairs = np.empty((max(cap, 1), 2), np.uint32)
     n = lib().orc_hamming_pairs(h, h.size, int(radius), pairs.reshape(-1), cap)
     return pairs[:min(n, cap)].copy(), int(n)
+
+
+def hamming_pairs_threaded(h, radius, cap=None, threads=None):
+    """The same all-pairs loop with its rows spread over host threads (row bands of equal
+    pair counts, concatenated in order): for inputs of 100,000+ hashes."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    h = np.ascontiguousarray(h, np.uint64)
+    n = h.size
+    cap = 1 << 20 if cap is None else cap
+    threads = threads or os.cpu_count() or 1
+    bands = threads * 8
+    # row i carries n-1-i pairs: cut the triangle into bands of equal area
+    edges = [int(round(n * (1.0 - np.sqrt(1.0 - b / bands)))) for b in range(bands)] + [n]
+    L = lib()
+
+    def band(b):
+        buf = np.empty((max(cap, 1), 2), np.uint32)
+        c = L.orc_hamming_pairs_rows(h, n, int(radius), edges[b], edges[b + 1], buf.reshape(-1), cap)
+        return buf[:min(c, cap)].copy(), int(c)
+
+    with ThreadPoolExecutor(threads) as ex:
+        parts = list(ex.map(band, range(bands)))
+    total = sum(c for _, c in parts)
+    allp = np.concatenate([p for p, _ in parts]) if parts else np.zeros((0, 2), np.uint32)
+    return allp[:cap], total
 
 
 def hamming_scan(h, q) -> np.ndarray:

@@ -447,12 +447,13 @@ ORC_API int orc_topk_f32(const float *scores, const int32_t *ids, int64_t n, int
 /* 64-bit Hamming (no counterpart in the reference)                          */
 /* ------------------------------------------------------------------------- */
 
-/* All pairs i<j with popcount(h[i]^h[j]) <= radius, in lexicographic (i,j) order.
- * Writes at most cap pairs; returns the total found. */
-ORC_API int64_t orc_hamming_pairs(const uint64_t *h, int64_t n, int radius,
-                                  uint32_t *pairs, int64_t cap) {
+/* All pairs i<j with popcount(h[i]^h[j]) <= radius whose i lies in [i_lo, i_hi), in
+ * lexicographic (i,j) order.  Writes at most cap pairs; returns the number found.  Row ranges
+ * are independent, so a caller may run several on threads and concatenate them in order. */
+ORC_API int64_t orc_hamming_pairs_rows(const uint64_t *h, int64_t n, int radius, int64_t i_lo, int64_t i_hi,
+                                       uint32_t *pairs, int64_t cap) {
     int64_t cnt = 0;
-    for (int64_t i = 0; i < n; i++) {
+    for (int64_t i = i_lo; i < i_hi && i < n; i++) {
         uint64_t a = h[i];
         for (int64_t j = i + 1; j < n; j++) {
             if (__builtin_popcountll(a ^ h[j]) <= radius) {
@@ -462,6 +463,13 @@ ORC_API int64_t orc_hamming_pairs(const uint64_t *h, int64_t n, int radius,
         }
     }
     return cnt;
+}
+
+/* All pairs i<j with popcount(h[i]^h[j]) <= radius, in lexicographic (i,j) order.
+ * Writes at most cap pairs; returns the total found. */
+ORC_API int64_t orc_hamming_pairs(const uint64_t *h, int64_t n, int radius,
+                                  uint32_t *pairs, int64_t cap) {
+    return orc_hamming_pairs_rows(h, n, radius, 0, n, pairs, cap);
 }
 
 /* One hash against n: distances out. */

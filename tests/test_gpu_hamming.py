@@ -40,6 +40,47 @@ def test_hamming_pairs_partitioned_union(lk):
     assert np.array_equal(packed, wpacked)
 
 
+def _pack(pairs):
+    return pairs[:, 0].astype(np.uint64) << np.uint64(32) | pairs[:, 1].astype(np.uint64)
+
+
+def _union(parts):
+    return np.sort(_pack(np.concatenate([p for p, _ in parts])))
+
+
+@pytest.fixture(scope="module")
+def big_set():
+    """200,000 hashes: buckets of the bit-field tables hold 400 (radius 6) to 3,000 (radius 9)
+    hashes, i.e. several 256-wide tiles each, the case where a split over callers depends on
+    every caller seeing the same bucket layout."""
+    h = phash_set(200_000, 77, max_flips=9)
+    return h, {r: O.hamming_pairs_threaded(h, r, cap=1 << 22) for r in (6, 9)}
+
+
+@pytest.mark.parametrize("radius", [6, 9])
+@pytest.mark.parametrize("parts", [2, 3, 8])
+def test_hamming_pairs_split_is_a_partition(lk, big_set, radius, parts):
+    h, want = big_set
+    wpairs, wtotal = want[radius]
+    single, cnt = lk.hamming_pairs(h, radius)
+    assert cnt == wtotal and np.array_equal(single, wpairs)
+    shares = [lk.hamming_pairs(h, radius, part=p, parts=parts) for p in range(parts)]
+    assert sum(c for _, c in shares) == wtotal
+    assert np.array_equal(_union(shares), _pack(wpairs))     # disjoint and complete
+    again = lk.hamming_pairs(h, radius, part=parts - 1, parts=parts)
+    assert np.array_equal(again[0], shares[-1][0])            # a share is the same on every call
+
+
+def test_hamming_pairs_split_repeats(lk, big_set):
+    """Twenty runs of the 3-way split at radius 9 (the case that used to lose or repeat a pair)."""
+    h, want = big_set
+    wpairs, wtotal = want[9]
+    for _ in range(20):
+        shares = [lk.hamming_pairs(h, 9, part=p, parts=3) for p in range(3)]
+        assert sum(c for _, c in shares) == wtotal
+        assert np.array_equal(_union(shares), _pack(wpairs))
+
+
 def test_hamming_pairs_cap(lk):
     h = phash_set(3000, 5)
     _, total = O.hamming_pairs(h, 6)
@@ -88,6 +129,10 @@ def test_hamming_full_size_properties(lk):
     lo, hi = np.minimum(a, b), np.maximum(a, b)
     planted = lo.astype(np.uint64) << np.uint64(32) | hi.astype(np.uint64)
     assert np.isin(planted, packed).all()
+    # the 8-way split (one share per GPU of a box) is a partition of that list
+    shares = [lk.hamming_pairs(h, 6, part=p, parts=8, cap=1 << 22) for p in range(8)]
+    assert sum(c for _, c in shares) == cnt
+    assert np.array_equal(_union(shares), packed)
 
 
 @pytest.mark.parametrize("radius", [0, 2, 3, 6, 9, 12, 20])
@@ -103,6 +148,7 @@ def test_hamming_pairs_indexed_and_swept_paths(lk, radius):
     assert np.array_equal(got, want)
     parts = [lk.hamming_pairs(h, radius, part=p, parts=3, cap=1 << 22) for p in range(3)]
     assert sum(c for _, c in parts) == total
+    assert np.array_equal(_union(parts), _pack(want))
 
 
 def test_hamming_pairs_skewed_buckets(lk):

@@ -52,6 +52,12 @@ for mode in ("nccl", "peer"):
             big = idx.search(queries[:1], 300)
             out[f"big_{name}_ids"] = big[0]
         rq.close(); idx.close()
+# duplicate detection split over the ranks: every rank ends up with the complete sorted list
+from tests.synth import phash_set
+h = phash_set(60000, 21, max_flips=9)
+for r in (6, 9):
+    out[f"ham{r}_pairs"], cnt = comm.hamming_pairs(h, r)
+    out[f"ham{r}_total"] = np.int64(cnt)
 np.savez(os.path.join(os.environ["LK_OUT"], f"rank{rank}.npz"), **out)
 dist.barrier()
 comm.close()
@@ -97,6 +103,13 @@ def test_sharded_search_over_nccl_equals_single_index(lk, tmp_path):
                 assert np.array_equal(g[f"{mode}_{name}_scores"], scores), (mode, name)
                 assert np.array_equal(g[f"{mode}_{name}_iscores"], iscores), (mode, name)
             assert np.array_equal(g[f"big_{name}_ids"], big), name
+    from tests.synth import phash_set
+    h = phash_set(60000, 21, max_flips=9)
+    for r in (6, 9):
+        pairs, total = lk.hamming_pairs(h, r)
+        for g in got:
+            assert int(g[f"ham{r}_total"]) == total
+            assert np.array_equal(g[f"ham{r}_pairs"], pairs)
 
 
 TIMEOUT_WORKER = r'''
