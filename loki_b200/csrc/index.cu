@@ -192,9 +192,9 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
     a.bound = nullptr;
     a.part = (unsigned long long *)idx->part.p;
     a.ticket = idx->d_ticket;
-    a.error = (int *)(idx->d_ticket + 1);
-    // consecutive launches may overlap at their edges: each uses its own batch counter
-    a.next_batch = idx->d_ticket + 2 + (idx->scan_launches & 3);
+    // consecutive launches may overlap at their edges: each uses its own batch counter and error word
+    a.error = (int *)(idx->d_ticket + 8 + (idx->scan_launches % kScanOverlap));
+    a.next_batch = idx->d_ticket + 2 + (idx->scan_launches % kScanOverlap);
     a.scales = idx->d_scales;
     a.qscale = qscale;
     a.shard_base = idx->shard_base;
@@ -223,7 +223,7 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
         a.out_count = res.d_counts() + (size_t)qi * passes + p;
         a.peer = peer;
         a.seq = seq;
-        LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream));
+        LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream, scan_may_overlap(idx->plan, idx->scan_launches)));
         idx->scan_launches++;
     }
     return 0;
@@ -390,7 +390,7 @@ static int search_one_fast(lk_index *idx, const float *query, int scoring, const
     a.seq = peer ? comm_next_seq(idx->comm) : 0u;
     a.done_flag = (unsigned int *)(z + off_flag);
     a.done_value = ++idx->zc_seq ? idx->zc_seq : ++idx->zc_seq;  // never 0
-    LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream));
+    LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream, scan_may_overlap(idx->plan, idx->scan_launches)));
     idx->scan_launches++;
     const auto t0 = std::chrono::steady_clock::now();
     for (unsigned spins = 0; *flag != a.done_value; ++spins) {

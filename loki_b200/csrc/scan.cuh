@@ -79,6 +79,7 @@ struct ScanPlan {
     int n_slabs = 1;       // stages per 32-row batch
     int fixed_chunks = 0;  // > 0: slab width (in 16-byte chunks) has a compile-time kernel
     size_t bulk_smem = 0;
+    int bulk_per_sm = 1;   // CTAs of the TMA-staged kernel one SM can hold (narrow rows: several)
     // TMA-staged kernel for wide rows (ld a multiple of 512 B, >= 1 KB): whole-row batches
     bool wide_ok = false;
     int wide_nj = 0;       // 512-byte units per row
@@ -86,10 +87,18 @@ struct ScanPlan {
     int wide_warps = 0;
     int wide_run = 1;      // consecutive batches handed out per counter access
     size_t wide_smem = 0;
+    int wide_per_sm = 1;
 };
 int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan);
 int scan_max_grid(const ScanPlan &plan);   // CTAs to size the per-CTA list scratch for
-int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream);
+// Consecutive launches of the TMA-staged kernels overlap at their edges (programmatic dependent
+// launch) and rotate over kScanOverlap batch counters and error words.  One SM holds one CTA of
+// the usual shapes, which limits the overlap to two launches by itself; where several CTAs fit
+// on an SM (narrow rows) the launch that reuses slot 0 is issued with plain stream order
+// (`overlap` false), so that never more than kScanOverlap launches are in flight.
+constexpr int kScanOverlap = 4;
+bool scan_may_overlap(const ScanPlan &plan, long long launch_index);
+int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream, bool overlap = true);
 
 // Merge, for each of nq queries, `lists` ranked key lists of k entries each (global
 // memory, zero padded) into one ranked result of k entries at out_*[q*k];

@@ -1124,18 +1124,27 @@ int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.wide_smem);
             if (e != cudaSuccess) return fail(4, std::string("scan plan (wide): ") + cudaGetErrorString(e));
             p.wide_ok = true;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&p.wide_per_sm, (const void *)pick_wide(type, p.wide_nj),
+                                                              p.wide_warps * 32, p.wide_smem);
+            if (e != cudaSuccess) return fail(4, std::string("scan plan (wide): ") + cudaGetErrorString(e));
         }
     }
     if (p.bulk_ok) {
         bulk_fn fn = pick_bulk(type, p);
         e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.bulk_smem);
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&p.bulk_per_sm, (const void *)fn, kBulkWarps * 32, p.bulk_smem);
         if (e != cudaSuccess) return fail(4, std::string("scan plan (bulk): ") + cudaGetErrorString(e));
     }
     *plan = p;
     return 0;
 }
 
-int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream) {
+bool scan_may_overlap(const ScanPlan &plan, long long launch_index) {
+    const bool several_per_sm = (plan.bulk_ok && plan.bulk_per_sm > 1) || (plan.wide_ok && plan.wide_per_sm > 1);
+    return !(several_per_sm && launch_index % kScanOverlap == 0);
+}
+
+int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream, bool overlap) {
     const long long batches = (a.n + 31) / 32;
     // the TMA-staged kernel needs whole, contiguous rows and enough batches to fill its pipeline
     const bool bulk = plan.bulk_ok && a.slots == nullptr && batches >= (long long)plan.bulk_grid * kBulkWarps;
@@ -1152,7 +1161,7 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = overlap ? 1 : 0;
         cudaError_t le = cudaLaunchKernelEx(&cfg, fn, a, plan.wide_run);
         if (le != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(le));
     } else if (bulk) {
@@ -1166,7 +1175,7 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = overlap ? 1 : 0;
         cudaError_t le = cudaLaunchKernelEx(&cfg, fn, a, plan.slab_bytes, plan.n_slabs);
         if (le != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(le));
     } else {
