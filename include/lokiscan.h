@@ -238,7 +238,8 @@ LK_API int lk_hamming_scan(const uint64_t *hashes, int64_t n, uint64_t query, in
  * scratch is a fixed array inside the library image, LK_PREALLOC_SCRATCH_BYTES per GPU
  * that loads the library, held until the process exits.  The call makes no cudaMalloc,
  * cudaFree or other allocating call; it enqueues on `stream` (a cudaStream_t, NULL =
- * default stream) and returns without waiting.
+ * default stream) and returns without waiting.  The caller's current device is the same after
+ * the call as before it.
  *   d_codes   n rows of int8 codes, ld bytes apart (ld a multiple of 16, padding zero),
  *             16-byte aligned: the layout lk_index_read_rows describes, kept on device
  *   d_scales  n per-row float scales (score = int dot * query_scale * row scale)

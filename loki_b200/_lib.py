@@ -227,6 +227,23 @@ class DeviceIndex:
                             ids.ctypes.data, scores.ctypes.data, iscores.ctypes.data, counts.ctypes.data))
         return ids, scores, iscores, counts
 
+    def search_one(self, query, k: int, scoring: int = LK_SCORE_DEFAULT):
+        """One query through lk_search with as little Python around the call as possible: the
+        output arrays are kept per k and reused, so the result is valid until the next call.
+        -> ids[1,k], scores[1,k], iscores[1,k], counts[1]."""
+        cache = self.__dict__.setdefault("_one", {})
+        b = cache.get(k)
+        if b is None:
+            arrs = (np.empty((1, k), np.int64), np.empty((1, k), np.float32), np.empty((1, k), np.int32), np.empty(1, np.int32))
+            b = cache[k] = (arrs, tuple(a.ctypes.data for a in arrs))
+        q = query if (query.dtype == np.float32 and query.flags["C_CONTIGUOUS"]) else np.ascontiguousarray(query, np.float32)
+        if q.size != self.dim:
+            raise LokiError(LK_EDIM, f"query has {q.size} elements, index has dim {self.dim}")
+        st = lib.lk_search(self._h, q.ctypes.data, 1, k, scoring, None, 0, *b[1])
+        if st != LK_OK:
+            check(st)
+        return b[0]
+
     def search_shared(self, pos, posw=None, neg=None, negw=None, k: int = 10, scoring: int = LK_SCORE_DEFAULT,
                       allow_slots=None, beta: float = 0.25, lam: float = 1.0):
         pos = np.ascontiguousarray(pos, dtype=np.float32).reshape(-1, self.dim) if len(pos) else np.zeros((0, self.dim), np.float32)

@@ -200,6 +200,11 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
     a.shard_base = idx->shard_base;
     a.peer = nullptr;
     a.seq = 0;
+    a.defer = 0;
+    a.d_out_ids = nullptr;
+    a.d_out_scores = nullptr;
+    a.d_out_iscores = nullptr;
+    a.d_out_count = nullptr;
     a.done_flag = nullptr;
     a.done_value = 0;
     return a;
@@ -209,7 +214,8 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
 // at most kMaxK; pass p accepts only keys below the last key of pass p-1.
 static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered, float cq, float qscale,
                          const int *d_slots, long long n_cand, int k_eff, int k_stride, int passes,
-                         const ResultArena &res, int qi, const PeerTable *peer = nullptr, unsigned int seq = 0) {
+                         const ResultArena &res, int qi, const PeerTable *peer = nullptr, unsigned int seq = 0,
+                         int batch_pos = 0) {
     for (int p = 0; p < passes; ++p) {
         const int done = p * kMaxK;
         ScanArgs a = base_args(idx, centered, cq, qscale, d_slots, n_cand, std::min(kMaxK, k_eff - done));
@@ -223,9 +229,41 @@ static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered,
         a.out_count = res.d_counts() + (size_t)qi * passes + p;
         a.peer = peer;
         a.seq = seq;
+        if (peer) {  // queued sharded scans: this launch merges the query kPeerDefer places back in the batch
+            a.defer = kPeerDefer;
+            if (batch_pos >= kPeerDefer) {
+                const size_t od = (size_t)(qi - kPeerDefer) * k_stride;
+                a.d_out_ids = res.d_ids() + od;
+                a.d_out_scores = res.d_scores() + od;
+                a.d_out_iscores = res.d_iscores() + od;
+                a.d_out_count = res.d_counts() + (size_t)(qi - kPeerDefer);
+            }
+        }
         LK_TRY(scan_launch(idx->type, a, idx->plan, idx->stream, scan_may_overlap(idx->plan, idx->scan_launches)));
         idx->scan_launches++;
     }
+    return 0;
+}
+
+// After `count` queued sharded scans whose last query has index qi_last and sequence number
+// seq_last: merge the queries that no later launch has merged.
+static int drain_queued(lk_index *idx, const PeerTable *peer, const ResultArena &res, int qi_last, unsigned int seq_last,
+                        int count, int k_eff) {
+    const int m = std::min(count, kPeerDefer);
+    if (m <= 0) return 0;
+    DrainArgs d;
+    d.peer = peer;
+    d.seq_first = seq_last - (unsigned)(m - 1);
+    d.count = m;
+    d.k = k_eff;
+    d.type = idx->type;
+    const size_t o = (size_t)(qi_last - (m - 1)) * k_eff;
+    d.out_ids = res.d_ids() + o;
+    d.out_scores = res.d_scores() + o;
+    d.out_iscores = res.d_iscores() + o;
+    d.out_count = res.d_counts() + (qi_last - (m - 1));
+    LK_TRY(peer_drain_launch(d, idx->stream));
+    idx->aux_launches++;
     return 0;
 }
 
@@ -698,10 +736,13 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
         d_slots = (const int *)idx->d_slots.p;
     }
     // sharded: exchange inside the scan kernel over peer memory when that is set up, else NCCL
-    for (int q = 0; q < nq; ++q)
+    unsigned int seq = 0;
+    for (int q = 0; q < nq; ++q) {
+        seq = peer ? comm_next_seq(idx->comm) : 0u;
         LK_TRY(enqueue_query(idx, (const unsigned char *)idx->d_query.p + (size_t)q * idx->qbytes, cen[q] != 0, cq[q],
-                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer,
-                             peer ? comm_next_seq(idx->comm) : 0u));
+                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer, seq, q));
+    }
+    if (peer) LK_TRY(drain_queued(idx, peer, idx->res, nq - 1, seq, nq, k_eff));
     if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
     LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
@@ -860,13 +901,15 @@ int lk_search_resident(lk_index *idx, lk_queries *q, int first, int count, int k
     LK_TRY(ensure_scan_scratch(idx, k_eff));
     if (q->res.nq != q->nq || q->res.k != k_eff) LK_TRY(q->res.shape(q->nq, k_eff, 1));
     const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
+    unsigned int seq = 0;
     for (int i = first; i < first + count; ++i) {
+        seq = peer ? comm_next_seq(idx->comm) : 0u;
         LK_TRY(enqueue_query(idx, (const unsigned char *)q->d_query.p + (size_t)i * idx->qbytes, q->centered != 0,
-                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i, peer,
-                             peer ? comm_next_seq(idx->comm) : 0u));
+                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i, peer, seq, i - first));
         // one query at a time: without the peer path its candidates are gathered and merged here
         if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, q->res, i, 1, k_eff));
     }
+    if (peer) LK_TRY(drain_queued(idx, peer, q->res, first + count - 1, seq, count, k_eff));
     return LK_OK;
 }
 

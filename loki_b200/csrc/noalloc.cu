@@ -49,6 +49,15 @@ static int prealloc_scratch(int device, unsigned char **out) {
     return 0;
 }
 
+// The hosts this entry point is for live inside someone else's runtime: put the caller's
+// current device back when the call ends.
+struct DeviceRestore {
+    int prev = -1;
+    ~DeviceRestore() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
 }  // namespace lk
 
 using namespace lk;
@@ -68,7 +77,10 @@ extern "C" int lk_scan_i8_prealloc(int device, const int8_t *d_codes, int64_t n,
     if (n > 0xfffffff0ll) return fail(LK_ERANGE, "lk_scan_i8_prealloc: more than 2^32-16 rows");
     if (device < 0 || device >= kPreMaxDevices || device >= lk_device_count())
         return fail(LK_ECUDA, "lk_scan_i8_prealloc: no such CUDA device (this library has no CPU path)");
-    LK_CUDA(cudaSetDevice(device));
+    DeviceRestore restore;
+    if (cudaGetDevice(&restore.prev) != cudaSuccess) restore.prev = -1;
+    if (restore.prev == device) restore.prev = -1;  // nothing to put back
+    else LK_CUDA(cudaSetDevice(device));
     unsigned char *scratch = nullptr;
     LK_TRY(prealloc_scratch(device, &scratch));
     ScanPlan plan;

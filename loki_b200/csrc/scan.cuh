@@ -7,12 +7,13 @@ namespace lk {
 
 // Direct exchange of per-shard results between the GPUs of one box (peer memory over
 // NVLink): every rank owns an inbox that all ranks can write.
-constexpr int kPeerSlots = 4;    // queries in flight before an inbox slot is reused
+constexpr int kPeerSlots = 8;    // queries in flight before an inbox slot is reused (>= 2 * kPeerDefer + 2)
+constexpr int kPeerDefer = 3;    // queued scans: a launch merges the query issued this many launches earlier
 constexpr int kPeerMaxWorld = 16;
 constexpr int kPeerMaxK = 128;   // larger k goes through the NCCL all-gather
 struct PeerInbox {
-    unsigned int flags[kPeerSlots][kPeerMaxWorld];                    // sequence number of the list present
-    unsigned int pad[64 - (kPeerSlots * kPeerMaxWorld) % 64];
+    unsigned int flags[kPeerSlots][kPeerMaxWorld];                    // tag of the list present (peer_tag)
+    unsigned int pad[64];
     unsigned long long keys[kPeerSlots][kPeerMaxWorld][kPeerMaxK];    // ranked keys, GLOBAL row ids
     float payload[kPeerSlots][kPeerMaxWorld][kPeerMaxK];              // finished float score of int8 hits
 };
@@ -50,6 +51,17 @@ struct ScanArgs {
     long long shard_base;
     const PeerTable *peer;      // nullptr, or: exchange the result with the other shards inside the kernel
     unsigned int seq;           // sequence number of this query, the same on every rank
+    // Which query this launch merges once its own list is published.  defer == 0: its own, i.e. it
+    // waits until every shard's list for this query has arrived (a caller that needs the answer
+    // now).  defer == kPeerDefer (queued scans): the query issued that many launches earlier, whose
+    // outputs are d_out_* (nullptr: none, the first launches of a batch); a rank then stalls only
+    // when another rank is more than kPeerDefer queries behind, and peer_drain_launch merges the
+    // last queries of the batch.
+    int defer;
+    long long *d_out_ids;
+    float *d_out_scores;
+    int *d_out_iscores;
+    int *d_out_count;
     // Low-latency single query: outputs may point into mapped pinned host memory; after they
     // are written the kernel releases *done_flag = done_value for a host that is polling it.
     unsigned int *done_flag;    // nullptr = none
@@ -99,6 +111,19 @@ int scan_max_grid(const ScanPlan &plan);   // CTAs to size the per-CTA list scra
 constexpr int kScanOverlap = 4;
 bool scan_may_overlap(const ScanPlan &plan, long long launch_index);
 int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream, bool overlap = true);
+
+// After a batch of queued sharded scans: merge queries seq_first .. seq_first+count-1 (count <=
+// kPeerDefer) from this rank's inbox into out_*[i*k], one CTA, plain stream order.
+struct DrainArgs {
+    const PeerTable *peer;
+    unsigned int seq_first;
+    int count, k, type;
+    long long *out_ids;
+    float *out_scores;
+    int *out_iscores;
+    int *out_count;
+};
+int peer_drain_launch(const DrainArgs &a, cudaStream_t stream);
 
 // Merge, for each of nq queries, `lists` ranked key lists of k entries each (global
 // memory, zero padded) into one ranked result of k entries at out_*[q*k];

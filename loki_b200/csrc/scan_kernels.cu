@@ -259,6 +259,85 @@ __device__ __forceinline__ void slab_accumulate_fixed(typename TR::acc_t (&acc)[
 
 constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // longest wait for another rank's list: 2 s
 
+// Tag a rank stores into a slot's flag once its list for query `seq` is complete: never 0
+// (the flags start at 0); the top bit says that the rank's own scan failed (a bounded wait
+// ran out), which makes the query invalid on every rank.
+constexpr unsigned kPeerPoison = 0x80000000u;
+__device__ __forceinline__ unsigned peer_tag(unsigned seq) { return seq % 0x7ffffffeu + 1u; }
+
+// Wait (bounded) until every rank's list for query `seq` has landed in this rank's inbox, merge
+// them into `buf` and write the global result.  Called by all threads of one CTA.  Returns the
+// number of hits, or -1 when a rank did not deliver in time or delivered a failed scan.
+template <int TYPE>
+__device__ __forceinline__ int peer_merge_emit(const PeerTable &pt, unsigned seq, int k, const CandBuf &buf,
+                                               long long *out_ids, float *out_scores, int *out_iscores) {
+    const int tid = threadIdx.x, T = blockDim.x;
+    const int slot = (int)(seq % kPeerSlots);
+    const unsigned want = peer_tag(seq);
+    __shared__ int s_peer_bad;
+    __syncthreads();
+    if (tid == 0) s_peer_bad = 0;
+    __syncthreads();
+    if (tid < pt.world) {
+        const unsigned int *f = &pt.inbox[pt.rank]->flags[slot][tid];
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v == want) break;
+            if (v == (want | kPeerPoison)) {
+                s_peer_bad = 1;
+                break;
+            }
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > kPeerWaitNs) {  // a rank never delivered: give up, report, stay usable
+                s_peer_bad = 1;
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    const bool bad = s_peer_bad != 0;
+    const PeerInbox *mine_in = pt.inbox[pt.rank];
+    cand_select_from_lists(buf, &mine_in->keys[slot][0][0], pt.world, kPeerMaxK);
+    const int cnt = buf.ctrl->count;
+    for (int i = tid; i < k; i += T) {
+        const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
+        if (key == 0ull) {
+            emit_hit(TYPE, 0ull, i, 0, 0.0f, out_ids, out_scores, out_iscores);
+            continue;
+        }
+        out_ids[i] = (long long)key_slot(key);  // already a global row number
+        if (TYPE != SCAN_I8) {
+            out_scores[i] = f32_from_ord(key_ord(key));
+            if (out_iscores) out_iscores[i] = 0;
+            continue;
+        }
+        // the float score was finished by the shard owning the row: find the key in the lists
+        float sc = 0.0f;
+        bool found = false;
+        for (int r = 0; r < pt.world && !found; ++r) {
+            int lo = 0, hi = k - 1;
+            while (lo <= hi) {  // ranked descending
+                const int mid = (lo + hi) >> 1;
+                const unsigned long long v = __ldcg(&mine_in->keys[slot][r][mid]);
+                if (v == key) {
+                    sc = __ldcg(&mine_in->payload[slot][r][mid]);
+                    found = true;
+                    break;
+                }
+                if (v > key) lo = mid + 1; else hi = mid - 1;
+            }
+        }
+        out_scores[i] = sc;
+        if (out_iscores) out_iscores[i] = i32_from_ord(key_ord(key));
+    }
+    __syncthreads();
+    return bad ? -1 : cnt;
+}
+
 // Shared tail of both scan kernels: publish this CTA's list; the last CTA to arrive
 // merges all lists and writes the result.
 template <int TYPE>
@@ -274,7 +353,9 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
     __threadfence();
     cand_select_from_lists(buf, a.part, (int)gridDim.x);
     int cnt = buf.ctrl->count;
-    bool peer_timeout = false;
+    // a CTA whose bounded wait ran out has raised the flag before publishing its list
+    const bool scan_bad = a.error != nullptr && *(volatile int *)a.error != 0;
+    int *count_to = a.out_count;
     if (a.peer == nullptr) {
         for (int i = tid; i < a.k; i += T) {
             const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
@@ -283,15 +364,16 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
             if (TYPE == SCAN_I8 && key != 0ull) dq = a.qscale * a.scales[key_slot(key)];
             emit_hit(TYPE, key, i, a.shard_base, dq, a.out_ids, a.out_scores, a.out_iscores);
         }
+        if (scan_bad) cnt = -1;
     } else {
         // ---- sharded index: exchange with the other GPUs of the box, then merge ----
         // This shard's ranked list goes straight into every rank's inbox over NVLink
-        // (plain stores to peer memory), followed by a release of the slot's flag; then
-        // this CTA waits (bounded) until all ranks' lists for this query have landed in
-        // its own inbox and merges them.  No collective launch, no host round trip.
+        // (plain stores to peer memory), followed by a release of the slot's flag.  Then this
+        // CTA waits (bounded) until all ranks' lists for the query it is to merge have landed
+        // in its own inbox and merges them.  No collective launch, no host round trip.
         const PeerTable &pt = *a.peer;
         const int slot = (int)(a.seq % kPeerSlots);
-        const unsigned want = a.seq + 1u;
+        const unsigned tag = peer_tag(a.seq) | (scan_bad ? kPeerPoison : 0u);
         for (int i = tid; i < a.k; i += T) {
             const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
             a.out_keys[i] = key;
@@ -309,62 +391,15 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
         __syncthreads();
         if (tid < pt.world) {
             unsigned int *f = &pt.inbox[tid]->flags[slot][pt.rank];
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(want) : "memory");
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tag) : "memory");
         }
-        __shared__ int s_peer_bad;
-        if (tid == 0) s_peer_bad = 0;
-        __syncthreads();
-        if (tid < pt.world) {
-            const unsigned int *f = &pt.inbox[pt.rank]->flags[slot][tid];
-            unsigned long long t0, t1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-            for (;;) {
-                unsigned v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                if (v == want) break;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                if (t1 - t0 > kPeerWaitNs) {  // a rank never delivered: give up, report, stay usable
-                    s_peer_bad = 1;
-                    break;
-                }
-                __nanosleep(200);
-            }
-        }
-        __syncthreads();
-        peer_timeout = s_peer_bad != 0;
-        const PeerInbox *mine_in = pt.inbox[pt.rank];
-        cand_select_from_lists(buf, &mine_in->keys[slot][0][0], pt.world, kPeerMaxK);
-        cnt = buf.ctrl->count;
-        for (int i = tid; i < a.k; i += T) {
-            const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
-            if (key == 0ull) {
-                emit_hit(TYPE, 0ull, i, 0, 0.0f, a.out_ids, a.out_scores, a.out_iscores);
-                continue;
-            }
-            a.out_ids[i] = (long long)key_slot(key);  // already a global row number
-            if (TYPE != SCAN_I8) {
-                a.out_scores[i] = f32_from_ord(key_ord(key));
-                if (a.out_iscores) a.out_iscores[i] = 0;
-                continue;
-            }
-            // the float score was finished by the shard owning the row: find the key in the lists
-            float sc = 0.0f;
-            bool found = false;
-            for (int r = 0; r < pt.world && !found; ++r) {
-                int lo = 0, hi = a.k - 1;
-                while (lo <= hi) {  // ranked descending
-                    const int mid = (lo + hi) >> 1;
-                    const unsigned long long v = __ldcg(&mine_in->keys[slot][r][mid]);
-                    if (v == key) {
-                        sc = __ldcg(&mine_in->payload[slot][r][mid]);
-                        found = true;
-                        break;
-                    }
-                    if (v > key) lo = mid + 1; else hi = mid - 1;
-                }
-            }
-            a.out_scores[i] = sc;
-            if (a.out_iscores) a.out_iscores[i] = i32_from_ord(key_ord(key));
+        if (a.defer == 0) {
+            cnt = peer_merge_emit<TYPE>(pt, a.seq, a.k, buf, a.out_ids, a.out_scores, a.out_iscores);
+        } else if (a.d_out_ids != nullptr) {
+            cnt = peer_merge_emit<TYPE>(pt, a.seq - (unsigned)a.defer, a.k, buf, a.d_out_ids, a.d_out_scores, a.d_out_iscores);
+            count_to = a.d_out_count;
+        } else {
+            count_to = nullptr;  // merged later, by a following launch or the drain
         }
     }
     if (a.done_flag != nullptr) {  // results may sit in host memory: make them visible there first
@@ -372,9 +407,7 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
         __syncthreads();
     }
     if (tid == 0) {
-        // a CTA whose bounded wait ran out has raised the flag before publishing its list
-        const bool bad = (a.error != nullptr && *(volatile int *)a.error != 0) || peer_timeout;
-        *a.out_count = bad ? -1 : cnt;
+        if (count_to != nullptr) *count_to = cnt;
         if (a.error != nullptr) *a.error = 0;
         if (a.next_batch != nullptr) *a.next_batch = 0u;
         *a.ticket = 0u;
@@ -382,6 +415,23 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
             __threadfence_system();
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.done_flag), "r"(a.done_value) : "memory");
         }
+    }
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(kScanThreads, 1) k_peer_drain(const DrainArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    CandBuf buf;
+    buf.k = a.k;
+    buf.cap = cand_capacity(a.k);
+    buf.limit = buf.cap - kScanThreads;
+    buf.keys = reinterpret_cast<unsigned long long *>(smem);
+    buf.ctrl = reinterpret_cast<CandCtrl *>(smem + (size_t)buf.cap * 8);
+    for (int q = 0; q < a.count; ++q) {
+        const size_t o = (size_t)q * a.k;
+        const int cnt = peer_merge_emit<TYPE>(*a.peer, a.seq_first + (unsigned)q, a.k, buf, a.out_ids + o, a.out_scores + o,
+                                              a.out_iscores ? a.out_iscores + o : nullptr);
+        if (threadIdx.x == 0) a.out_count[q] = cnt;
     }
 }
 
@@ -1186,6 +1236,15 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(e));
+    return 0;
+}
+
+int peer_drain_launch(const DrainArgs &a, cudaStream_t stream) {
+    const size_t smem = (size_t)cand_capacity(a.k) * 8 + 16;
+    void (*fn)(const DrainArgs) = a.type == SCAN_I8 ? k_peer_drain<SCAN_I8> : (a.type == SCAN_F32 ? k_peer_drain<SCAN_F32> : k_peer_drain<SCAN_F16>);
+    fn<<<1, kScanThreads, smem, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(4, std::string("drain launch: ") + cudaGetErrorString(e));
     return 0;
 }
 

@@ -223,15 +223,28 @@ def build_i8(rows, ld_out=None):
     return codes, scales
 
 
-def scan_i8(codes, q, d=None, slots=None) -> np.ndarray:
+def scan_i8(codes, q, d=None, slots=None, workers=1) -> np.ndarray:
+    """int32 dot of every row (or rows[slots[t]]) with q; workers > 1 splits the rows into
+    contiguous bands, one host thread each (whole-corpus scans of 1,000,000+ rows)."""
     codes = np.ascontiguousarray(codes, np.int8)
     q = np.ascontiguousarray(q, np.int8)
     d = q.size if d is None else d
     n = codes.shape[0] if slots is None else len(slots)
     out = np.empty(n, np.int32)
     sl = None if slots is None else np.ascontiguousarray(slots, np.int32)
-    if n:
+    if n and (workers <= 1 or slots is not None or n < 4 * workers):
         lib().orc_scan_i8(codes, codes.shape[1], d, q, _ptr(sl), n, out)
+    elif n:
+        from concurrent.futures import ThreadPoolExecutor
+        L = lib()
+        edges = [n * w // workers for w in range(workers + 1)]
+
+        def band(w):
+            lo, hi = edges[w], edges[w + 1]
+            L.orc_scan_i8(codes[lo:hi], codes.shape[1], d, q, None, hi - lo, out[lo:hi])
+
+        with ThreadPoolExecutor(workers) as ex:
+            list(ex.map(band, range(workers)))
     return out
 
 

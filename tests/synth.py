@@ -79,3 +79,40 @@ SEED_SCORING_CASES = [
     ("single candidate", 1, 300, 4, 64, 0.42, True, True, True),
     ("fewer candidates than the group width", 3, 300, 4, 64, 0.42, True, True, True),
 ]
+
+
+def device_corpus(lk, n: int, dim: int, store: int, seed: int, clustered: bool = False, centres: int = 256,
+                  sigma: float = 0.1, sample_every: int = 4099, chunk: int = 62_500, device: int = 0):
+    """A corpus of a benchmark configuration's full size, generated on the GPU in chunks
+    (seeded N(0,1); with `clustered` the odd rows sit around un-normalised Gaussian centres) and
+    handed to the index as device rows, so that no multi-gigabyte float array crosses the host.
+    Returns (index, sample_ids, sample_rows): the float32 input of every `sample_every`-th row,
+    kept on the host to check the stored form of those rows against the oracle."""
+    import torch
+
+    dev = torch.device("cuda", device)
+    idx = lk.DeviceIndex(dim, store, device=device)
+    idx.reserve(n)
+    gen = torch.Generator(device=dev)
+    cen = None
+    if clustered:
+        gen.manual_seed(seed + 2000)
+        cen = torch.randn((centres, dim), generator=gen, device=dev, dtype=torch.float32)
+    ids, rows = [], []
+    for c0 in range(0, n, chunk):
+        m = min(chunk, n - c0)
+        gen.manual_seed(seed * 1_000_003 + c0)
+        block = torch.randn((m, dim), generator=gen, device=dev, dtype=torch.float32)
+        if clustered:
+            gid = torch.arange(c0, c0 + m, device=dev)
+            odd = (gid % 2) == 1
+            block[odd] = cen[(gid[odd] // 2) % centres] + sigma * block[odd]
+        torch.cuda.synchronize(dev)
+        idx.upsert_device(c0, m, block.data_ptr())
+        pick = np.arange((-c0) % sample_every, m, sample_every)
+        if pick.size:
+            ids.append(pick + c0)
+            rows.append(block[torch.as_tensor(pick, device=dev)].cpu().numpy())
+        del block
+    assert len(idx) == n
+    return idx, np.concatenate(ids), np.concatenate(rows)

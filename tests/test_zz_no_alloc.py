@@ -1,14 +1,12 @@
 """GPU: the allocation-free scan entry point (lk_scan_i8_prealloc) against lk_search.
 
-Collected last on purpose (the file name sorts after every other test file): a run
-that stops at the first failure has then already run everything else.
-
 The entry point exists for hosts that may not allocate device memory while serving
 (a fixed GPU budget handed out at start-up, a latency path that cannot take the
 device-wide stall of cudaMalloc, a plug-in inside someone else's memory arena).  Here
 the test owns all buffers (torch tensors) and checks that two calls in a row, which
 share the library's built-in scratch array, each reproduce the regular search bit for
-bit: ids, raw int32 dots and de-quantised float scores.
+bit: ids, raw int32 dots and de-quantised float scores, and that the calls leave the amount
+of free device memory where it was.
 """
 import ctypes as C
 
@@ -30,7 +28,7 @@ def _prepared_query(lk, q, dim):
     return codes[0], float(scales[0])
 
 
-@pytest.mark.parametrize("n,dim,k", [(40_000, 768, 10), (3_000, 100, 128)])
+@pytest.mark.parametrize("n,dim,k", [(40_000, 768, 10), (3_000, 100, 128), (40_000, 1024, 50)])
 def test_prealloc_scan_matches_search_twice(lk, n, dim, k):
     import torch
 
@@ -53,18 +51,27 @@ def test_prealloc_scan_matches_search_twice(lk, n, dim, k):
     d_count = torch.empty(1, dtype=torch.int32, device=dev)
     torch.cuda.synchronize()
 
-    for qi in range(2):  # two calls in a row share the built-in scratch array
-        qcodes, qscale = _prepared_query(lk, queries[qi], dim)
+    prepared = [_prepared_query(lk, queries[qi], dim) for qi in range(2)]
+    d_queries = []
+    for qcodes, _ in prepared:
         qpad = np.zeros(ld, np.int8)
         qpad[:dim] = qcodes
-        d_query = torch.from_numpy(qpad).to(dev)
-        torch.cuda.synchronize()
+        d_queries.append(torch.from_numpy(qpad).to(dev))
+    torch.cuda.synchronize()
+    free_before = None
+    for qi in range(2):  # two calls in a row share the built-in scratch array
+        qscale = prepared[qi][1]
+        d_query = d_queries[qi]
+        if qi == 1:      # the first call has set the entry point up; from here on nothing may be allocated
+            free_before = torch.cuda.mem_get_info(dev)[0]
         st = lk.lib.lk_scan_i8_prealloc(0, C.c_void_p(d_codes.data_ptr()), n, dim, ld, C.c_void_p(d_scales.data_ptr()),
                                         C.c_void_p(d_query.data_ptr()), C.c_float(qscale), k,
                                         C.c_void_p(d_ids.data_ptr()), C.c_void_p(d_scores.data_ptr()),
                                         C.c_void_p(d_iscores.data_ptr()), C.c_void_p(d_count.data_ptr()), None)
         lk.check(st)
         torch.cuda.synchronize()
+        if qi == 1:
+            assert torch.cuda.mem_get_info(dev)[0] == free_before, "the call changed the free device memory"
         assert int(d_count.item()) == want_counts[qi] == k
         assert np.array_equal(d_ids.cpu().numpy(), want_ids[qi])
         assert np.array_equal(d_iscores.cpu().numpy(), want_iscores[qi])
