@@ -148,6 +148,19 @@ LK_API int lk_search_shared(lk_index *idx, const float *pos, const float *posw, 
                             const int32_t *allow_slots, int64_t n_allow,
                             int64_t *out_ids, float *out_scores, int32_t *out_count);
 
+/* Replaces the brute-force loops of the service layer, which run when no index is installed for a
+ * model or a face search is restricted to a set of media paths
+ * (media-server/tasks/embed_task.go:249-272, media-server/tasks/face_search.go:199-216, :235-248):
+ * embedvec.CosineSim (media-server/embedvec/embedvec.go:127-141) of one query against n RAW rows
+ * (host memory, n*dim floats, as the database holds them: not normalised), exact top-k.
+ * score = float32(dot / (sqrt(|q|^2) * sqrt(|v|^2))) in float64, 0 when either vector is all
+ * zero.  allow_slots as in lk_search.  Rank order: score descending, row number ascending on
+ * equal scores (pass the rows sorted by path to get the reference's path order among ties).
+ * Any k: more than 2,048 hits are selected in passes over the uploaded rows. */
+LK_API int lk_cosine_sim_topk(const float *rows, int64_t n, int dim, const float *query, int k,
+                              const int32_t *allow_slots, int64_t n_allow, int device,
+                              int64_t *out_ids, float *out_scores, int32_t *out_count);
+
 /* On-disk cache of a built index, replacing the rebuild from SQLite BLOBs at every start
  * (media-server/tasks/embed_task.go:189-210: LoadAllEmbeddings, then one Add per row).  The file
  * holds the index as it sits in device memory (normalised or quantised rows, scales, the

@@ -17,7 +17,7 @@ except Exception:  # pragma: no cover - torch is optional for this package
     torch = None
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("LOKI_B200_LIB", os.path.join(_HERE, "liblokiscan.so"))  # override: tuning builds only
+LIB_PATH = os.path.join(_HERE, "liblokiscan.so")
 
 LK_OK, LK_EINVAL, LK_EDIM, LK_ENOMEM, LK_ECUDA, LK_ENCCL, LK_ETIMEOUT, LK_ERANGE = range(8)
 LK_F32, LK_F16, LK_I8 = 0, 1, 2
@@ -92,6 +92,7 @@ _sig("lk_comm_peer_export", _int, _vp, _vp)
 _sig("lk_comm_peer_attach", _int, _vp, _vp)
 _sig("lk_index_attach_comm", _int, _vp, _vp, _i64)
 _sig("lk_index_set_shard_base", _int, _vp, _i64)
+_sig("lk_cosine_sim_topk", _int, _vp, _i64, _int, _vp, _int, _vp, _i64, _int, _vp, _vp, _vp)
 _sig("lk_hamming_pairs", _int, _vp, _i64, _int, _int, _int, _int, _vp, _i64, C.POINTER(_i64))
 _sig("lk_hamming_pairs_sharded", _int, _vp, _vp, _i64, _int, _vp, _i64, C.POINTER(_i64))
 _sig("lk_hamming_scan", _int, _vp, _i64, C.c_uint64, _int, _int, _vp, _vp, _i64, C.POINTER(_i64))
@@ -370,6 +371,28 @@ class Comm:
         if getattr(self, "_h", None):
             lib.lk_comm_destroy(self._h)
             self._h = None
+
+
+def cosine_sim_topk(rows, query, k: int, allow_slots=None, device: int = 0):
+    """embedvec.CosineSim of `query` against raw (un-normalised) rows, exact top-k:
+    -> (ids[m] int64, scores[m] float32), m = min(k, candidates)."""
+    r = np.ascontiguousarray(rows, dtype=np.float32)
+    q = np.ascontiguousarray(query, dtype=np.float32).reshape(-1)
+    n = r.shape[0]
+    dim = r.shape[1] if r.ndim == 2 and n else q.size
+    kk = max(int(k), 0)
+    ids = np.full(max(kk, 1), -1, np.int64)
+    scores = np.zeros(max(kk, 1), np.float32)
+    cnt = _int(0)
+    al, nal = None, 0
+    if allow_slots is not None:
+        al = np.ascontiguousarray(allow_slots, dtype=np.int32)
+        nal = al.size
+        if nal == 0:
+            al = np.zeros(1, np.int32)
+    check(lib.lk_cosine_sim_topk(ptr(r) if n else None, n, int(dim), ptr(q), int(k), ptr(al), nal, int(device),
+                                 ptr(ids), ptr(scores), C.byref(cnt)))
+    return ids[:cnt.value].copy(), scores[:cnt.value].copy()
 
 
 def hamming_pairs(hashes, radius: int, cap: int = 1 << 22, part: int = 0, parts: int = 1, device: int = 0):

@@ -13,8 +13,8 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OBJ = os.environ.get("LOKI_B200_OBJ", os.path.join(HERE, "build"))
-LIB = os.environ.get("LOKI_B200_LIB", os.path.join(HERE, "liblokiscan.so"))  # override: tuning builds only
+OBJ = os.path.join(HERE, "build")
+LIB = os.path.join(HERE, "liblokiscan.so")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -37,7 +37,7 @@ def _deps_mtime() -> float:
 
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
-    cmd = [NVCC, *ARCH, *COMMON, *os.environ.get("LOKI_B200_NVCC_FLAGS", "").split(), "-c", os.path.join(CSRC, src), "-o", obj]
+    cmd = [NVCC, *ARCH, *COMMON, "-c", os.path.join(CSRC, src), "-o", obj]
     if src.endswith(".cpp"):
         cmd.insert(1, "-x")
         cmd.insert(2, "cu")

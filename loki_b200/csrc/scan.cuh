@@ -112,6 +112,10 @@ constexpr int kScanOverlap = 4;
 bool scan_may_overlap(const ScanPlan &plan, long long launch_index);
 int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t stream, bool overlap = true);
 
+// Brute-force CosineSim scan over raw float rows (scan_kernels.cu).  With a.part == nullptr
+// only *grid_out is computed (to size the per-CTA list scratch: grid x k keys).
+int cosine_sim_launch(const ScanArgs &a, int dim, double q_n2, int sm_count, cudaStream_t stream, int *grid_out);
+
 // After a batch of queued sharded scans: merge queries seq_first .. seq_first+count-1 (count <=
 // kPeerDefer) from this rank's inbox into out_*[i*k], one CTA, plain stream order.
 struct DrainArgs {

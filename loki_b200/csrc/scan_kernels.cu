@@ -539,26 +539,12 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const __grid_constant_
 constexpr int kBulkStages = LK_BULK_STAGES;
 // SC > 0 fixes the slab width at compile time (SC 16-byte chunks, G must divide SC);
 // SC == 0 takes it from slab_bytes.  QREG keeps the query in registers (one slab per row).
-#ifdef LK_TIMELINE
-__device__ unsigned long long *g_timeline;  // [grid][8] nanosecond stamps (tuning builds only)
-__device__ __forceinline__ void tl_stamp(int i) {
-    if (threadIdx.x == 0 && g_timeline) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_timeline[blockIdx.x * 8 + i] = t;
-    }
-}
-#define LK_TL(i) tl_stamp(i)
-#else
-#define LK_TL(i)
-#endif
 
 template <class TR, int TYPE, int G, int WARPS, int SC, bool QREG>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_constant__ ScanArgs a, int slab_bytes_rt, int n_slabs_rt) {
     const int slab_bytes = SC > 0 ? SC * 16 : slab_bytes_rt;
     const int n_slabs = QREG ? 1 : n_slabs_rt;
     extern __shared__ __align__(128) unsigned char smem[];
-    LK_TL(0);
     constexpr int R = (G < 4) ? G : 4;  // shared-memory latency is short: few rows in flight suffice
     constexpr int T = WARPS * 32;
     using acc_t = typename TR::acc_t;
@@ -646,7 +632,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
     };
 #pragma unroll
     for (int s = 0; s < kBulkStages; ++s) issue(s);
-    LK_TL(1);
 
     // the rest of the prologue runs while the first copies are in flight
     for (int i = tid; i < buf.cap; i += T) buf.keys[i] = 0ull;
@@ -696,7 +681,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
                 failed = true;
                 continue;
             }
-            if (m == 0) LK_TL(2);
             const long long row0 = b << 5;
             const int rows = (int)min(32ll, a.n - row0);
             const int w = slab_width(sl);
@@ -737,10 +721,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
             cand_offer_warp(buf, valid && key > thr && key < bound, key);
             continue;
         }
-        if (!work) LK_TL(3);
         if (cand_rendezvous(buf, work, counted, lane, WARPS)) break;
     }
-    LK_TL(4);
     // A warp that gave up may still have copies in flight into its stages: wait for
     // them (bounded) before the CTA's shared memory is released.
     if (failed) {
@@ -760,7 +742,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
     // that launch has completely finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     publish_and_finish<TYPE>(a, buf, &s_last);
-    LK_TL(5);
 }
 
 // ---------------------------------------------------------------------------
@@ -946,6 +927,113 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     publish_and_finish<TYPE>(a, buf, &s_last);
+}
+
+// ---------------------------------------------------------------------------
+// Brute-force scan over RAW rows with the reference's CosineSim
+// (media-server/embedvec/embedvec.go:127-141): float32(dot / (sqrt(|q|^2) * sqrt(|v|^2))),
+// everything accumulated in float64, 0 when either vector is all zero.  This is the scoring
+// of the service layer's fallbacks, which run over the un-normalised vectors as the database
+// holds them (media-server/tasks/embed_task.go:249-272, media-server/tasks/face_search.go:199-216,
+// :235-248).  a.rows holds n_rows x dim floats, dim * 4 bytes apart (no padding, any alignment
+// of 4); a.query dim floats.  A warp takes 32 rows at a time, four rows in flight, all lanes on
+// one row; top-k and the final merge are the scan's.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kScanThreads, 2) k_cosine_sim(const __grid_constant__ ScanArgs a, int dim, double q_n2) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    CandBuf buf;
+    buf.k = a.k;
+    buf.cap = cand_capacity(a.k);
+    buf.limit = buf.cap - kScanThreads;
+    buf.keys = reinterpret_cast<unsigned long long *>(smem);
+    buf.ctrl = reinterpret_cast<CandCtrl *>(smem + (size_t)buf.cap * 8);
+    double *qs = reinterpret_cast<double *>(smem + (size_t)buf.cap * 8 + 16);
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < buf.cap; i += kScanThreads) buf.keys[i] = 0ull;
+    if (tid == 0) {
+        buf.ctrl->count = 0;
+        buf.ctrl->n_done = 0;
+        buf.ctrl->thr = 0ull;
+    }
+    const float *qf = reinterpret_cast<const float *>(a.query);
+    for (int j = tid; j < dim; j += kScanThreads) qs[j] = (double)qf[j];
+    const unsigned long long bound = a.bound ? __ldcg(a.bound) : ~0ull;  // later pass of a large-k search
+    __syncthreads();
+    const float *rows = reinterpret_cast<const float *>(a.rows);
+    const double q_norm = sqrt(q_n2);
+    const long long n_batches = (a.n + 31) >> 5;
+    const long long b_lo = n_batches * blockIdx.x / gridDim.x;
+    const long long b_hi = n_batches * (blockIdx.x + 1) / gridDim.x;
+    long long b = b_lo + warp;
+    bool counted = false;
+    for (;;) {
+        const bool work = b < b_hi;
+        int seen = 0;
+        if (lane == 0) seen = *(volatile int *)&buf.ctrl->count;
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (work && seen <= buf.limit) {
+            const long long row0 = b << 5;
+            int myslot = 0;
+            if (row0 + lane < a.n) myslot = a.slots ? a.slots[row0 + lane] : (int)(row0 + lane);
+            double my_dot = 0.0, my_n2 = 0.0;
+            for (int r0 = 0; r0 < 32; r0 += 4) {
+                const float *p[4];
+                double dot[4] = {0.0, 0.0, 0.0, 0.0}, n2[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int s = __shfl_sync(0xffffffffu, myslot, r0 + r);
+                    p[r] = rows + (size_t)s * dim;  // rows past the end alias row 0 and are dropped below
+                }
+                for (int j = lane; j < dim; j += 32) {
+                    const double q = qs[j];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const double v = (double)__ldg(p[r] + j);
+                        dot[r] = fma(v, q, dot[r]);   // float32 products are exact in float64
+                        n2[r] = fma(v, v, n2[r]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+#pragma unroll
+                    for (int w = 16; w >= 1; w >>= 1) {
+                        dot[r] += TraitsF32::shfl(dot[r], w);
+                        n2[r] += TraitsF32::shfl(n2[r], w);
+                    }
+                    if (lane == r0 + r) {
+                        my_dot = dot[r];
+                        my_n2 = n2[r];
+                    }
+                }
+            }
+            const bool valid = row0 + lane < a.n;
+            float score = 0.0f;
+            if (q_n2 != 0.0 && my_n2 != 0.0) score = (float)(my_dot / (q_norm * sqrt(my_n2)));
+            unsigned long long key = 0ull;
+            if (valid) key = make_key(ord_from_f32(score), (unsigned)myslot);
+            const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
+            cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            b += kScanWarps;
+            continue;
+        }
+        if (cand_rendezvous(buf, work, counted, lane, kScanWarps)) break;
+    }
+    publish_and_finish<SCAN_F32>(a, buf, &s_last);
+}
+
+int cosine_sim_launch(const ScanArgs &a, int dim, double q_n2, int sm_count, cudaStream_t stream, int *grid_out) {
+    const size_t smem = (size_t)cand_capacity(a.k) * 8 + 16 + (size_t)dim * 8;
+    cudaError_t e = cudaFuncSetAttribute((const void *)k_cosine_sim, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(4, std::string("cosine_sim attr: ") + cudaGetErrorString(e));
+    const long long batches = (a.n + 31) / 32;
+    const int grid = (int)std::max<long long>(1, std::min<long long>(batches, (long long)sm_count * 2));
+    if (grid_out) *grid_out = grid;
+    if (a.part == nullptr) return 0;  // sizing call
+    k_cosine_sim<<<grid, kScanThreads, smem, stream>>>(a, dim, q_n2);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(4, std::string("cosine_sim launch: ") + cudaGetErrorString(e));
+    return 0;
 }
 
 // ---------------------------------------------------------------------------

@@ -1,4 +1,6 @@
-"""Host side of the face-clustering sweeps, mirroring the reference's functions for them.
+"""Test mirror of the caller's side of the face-clustering sweeps (not part of the library: the
+Go caller keeps this decision loop; here it exists so that the device kernels can be tested
+through the same two functions the reference has).
 
 ``prescreenCandidates`` and ``scoreAgainstSeeds`` keep the names, argument meaning and
 results of media-server/tasks/face_cluster.go:1189-1285 and :1315-1462.  The dense
@@ -18,7 +20,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Set
 
 import numpy as np
 
-from . import _lib
+from loki_b200 import _lib
 
 # media-server/tasks/face_cluster.go:34-38, :47, :62
 corroborationSlack = np.float32(0.06)

@@ -46,7 +46,7 @@ def test_small_output_buffer_reports_the_needed_size(lk):
 
 @pytest.mark.parametrize("case", SEED_SCORING_CASES, ids=lambda c: c[0])
 def test_decisions_equal_the_oracle(lk, case):
-    from loki_b200 import face_cluster as F
+    from tests import face_cluster_host as F
     name, n_cand, n_seed, people, dims, thr, vetoes, cannot, users = case
     sc = seed_scoring_case(n_cand, n_seed, people, dims, vetoes, cannot, users, seed=len(name) * 31)
     faces = [F.Face(ID=i, Vec=v) for i, v in zip(sc["cand_ids"], sc["cand_vecs"])]
@@ -65,7 +65,7 @@ def test_decisions_equal_the_oracle(lk, case):
 
 
 def test_prescreen_mirror_matches_the_oracle(lk):
-    from loki_b200 import face_cluster as F
+    from tests import face_cluster_host as F
     rng = np.random.default_rng(42)
     v = rng.standard_normal((300, 64)).astype(np.float32)
     v[4::5] = v[3::5] + 0.05
