@@ -274,14 +274,15 @@ static int unpack_results(const ResultArena &res, int nq, int k_user, int k_eff,
 // top-k fused into its epilogue (gemm_i8.cu); same scores and ranking as query-by-query scans.
 static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, int k_eff, int64_t *out_ids,
                        float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
-    const int slices = gemm_max_slices(idx->sm_count, nq);
+    const int slices = gemm_max_slices(idx->sm_count, nq, idx->len);
     const size_t e = (size_t)nq * k_eff;
-    // device: queries | query scales | list bases (zeros) | lists [slices][nq][k] | merge scratch
+    // device: queries | query scales | list bases (zeros) | shared thresholds (zeros) | lists [slices][nq][k] | merge scratch
     const size_t q_bytes = (size_t)round_up((int64_t)nq * idx->qbytes, 256);
     const size_t qs_bytes = (size_t)round_up((int64_t)nq * 4, 256);
     const size_t base_bytes = (size_t)round_up((int64_t)slices * 8, 256);
+    const size_t thr_bytes = (size_t)round_up((int64_t)gemm_thr_bytes(nq), 256);
     const size_t list_bytes = (size_t)slices * e * 8;
-    LK_TRY(idx->d_query.reserve(q_bytes + qs_bytes + base_bytes + 2 * list_bytes));
+    LK_TRY(idx->d_query.reserve(q_bytes + qs_bytes + base_bytes + thr_bytes + 2 * list_bytes));
     LK_TRY(idx->gemm_cand.reserve(gemm_cand_bytes(idx->sm_count)));
     LK_TRY(idx->res.shape(nq, k_eff, 1));
     // Queries are prepared on the device by the same kernel that stores rows (a query is
@@ -293,10 +294,11 @@ static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, 
     LK_TRY(normalize_store_launch(LK_I8, (const float *)idx->d_stage.p, nq, idx->dim, dq, idx->ld,
                                   (float *)(dq + q_bytes), idx->sm_count, idx->stream));
     idx->aux_launches++;
-    LK_CUDA(cudaMemsetAsync(dq + q_bytes + qs_bytes, 0, base_bytes + list_bytes, idx->stream));
-    unsigned long long *d_lists = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes);
+    LK_CUDA(cudaMemsetAsync(dq + q_bytes + qs_bytes, 0, base_bytes + thr_bytes + list_bytes, idx->stream));
+    unsigned long long *d_gthr = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes);
+    unsigned long long *d_lists = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes + thr_bytes);
     int *d_err = (int *)(idx->d_ticket + 1);
-    LK_TRY(gemm_launch(idx->d_rows, idx->len, idx->ld, dq, nq, k_eff, (unsigned long long *)idx->gemm_cand.p, d_lists,
+    LK_TRY(gemm_launch(idx->d_rows, idx->len, idx->ld, dq, nq, k_eff, (unsigned long long *)idx->gemm_cand.p, d_gthr, d_lists,
                        d_err, idx->sm_count, idx->stream, &idx->aux_launches));
     MergeArgs m;
     m.keys = d_lists;
