@@ -470,6 +470,13 @@ static int unpack_results(const ResultArena &res, int nq, int k_user, int k_eff,
         for (int p = 0; p < passes; ++p) cnt += res.h_counts()[(size_t)q * passes + p];
         if (cnt > k_eff) cnt = k_eff;
         const size_t so = (size_t)q * res.k, uo = (size_t)q * k_user;
+        if (cnt == k_user) {  // the usual case: every place taken, whole rows move at once
+            if (out_ids) memcpy(out_ids + uo, res.h_ids() + so, sizeof(int64_t) * (size_t)k_user);
+            if (out_scores) memcpy(out_scores + uo, res.h_scores() + so, sizeof(float) * (size_t)k_user);
+            if (out_iscores) memcpy(out_iscores + uo, res.h_iscores() + so, sizeof(int32_t) * (size_t)k_user);
+            if (out_counts) out_counts[q] = cnt;
+            continue;
+        }
         for (int i = 0; i < k_user; ++i) {
             const bool hit = i < cnt;
             if (out_ids) out_ids[uo + i] = hit ? (int64_t)res.h_ids()[so + i] : -1;

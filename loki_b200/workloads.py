@@ -8,6 +8,7 @@
     python -m loki_b200.workloads faces  [--rows 20000 --seeds 50000 --dim 512]
     python -m loki_b200.workloads pca    [--rows 20000 --dim 768 --workers 8]
     python -m loki_b200.workloads cache  [--rows 1000000 --dim 768 --store i8]
+    python -m loki_b200.workloads i8peak [--rows 8192]      the int8 tensor rate the batched search is measured against
 
 The benchmark of the headline workload is `bench.py`; these are the other configurations,
 each printing what it ran and how long it took.  They are also the commands the profiler is
@@ -98,6 +99,40 @@ def run_gemm(a):
         ms = idx.timer_stop()
         print(f"gemm {a.queries} queries x {a.rows} x {a.dim} int8 k={a.k}: call {wall * 1e3:.2f} ms ({a.queries / wall:.0f} queries/s), "
               f"{ms:.2f} ms between stream events, {2.0 * a.queries * a.rows * a.dim / wall / 1e12:.0f} Tops/s over the call")
+
+
+def run_i8peak(a):
+    """The denominator for the batched int8 search: a plain int8 x int8 -> int32 matrix product of
+    the vendor library (torch._int_mm, rows^3), measured like the bf16 peak of this machine: the best
+    of ten single products (burst) and a back-to-back loop of about three seconds (sustained, under
+    the power cap).  The corpus-sized product of the batched search runs for milliseconds, in bursts
+    between host work: it is held against the burst figure."""
+    import torch
+    n = a.rows if a.rows and a.rows <= 16384 else 8192
+    dev = torch.device("cuda")
+    x = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+    y = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev).t()   # column-major right operand
+    ops = 2.0 * n * n * n
+    for _ in range(3):
+        torch._int_mm(x, y)
+    torch.cuda.synchronize()
+    best = 1e9
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(10):
+        e0.record()
+        torch._int_mm(x, y)
+        e1.record()
+        e1.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    reps = max(10, int(3000.0 / best))
+    e0.record()
+    for _ in range(reps):
+        torch._int_mm(x, y)
+    e1.record()
+    e1.synchronize()
+    sustained = e0.elapsed_time(e1) / reps
+    print(f"i8peak {n}^3 int8 -> int32 (torch._int_mm): burst {best:.3f} ms = {ops / best / 1e9:.0f} Tops/s; "
+          f"sustained over {reps} products {sustained:.3f} ms = {ops / sustained / 1e9:.0f} Tops/s")
 
 
 def run_multi(a):
@@ -200,7 +235,7 @@ def run_cache(a):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m loki_b200.workloads", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("workload", choices=["scan", "gemm", "multi", "shared", "hamming", "faces", "pca", "cache"])
+    ap.add_argument("workload", choices=["scan", "gemm", "multi", "shared", "hamming", "faces", "pca", "cache", "i8peak"])
     ap.add_argument("--rows", type=int)
     ap.add_argument("--dim", type=int)
     ap.add_argument("--store", default="i8", choices=sorted(STORES))
@@ -215,13 +250,13 @@ def main(argv=None):
     a = ap.parse_args(argv)
     defaults = {"scan": (1_000_000, 768, 10, 0), "gemm": (2_000_000, 768, 100, 4096), "multi": (1_000_000, 768, 10, 64),
                 "shared": (1_000_000, 768, 50, 0), "hamming": (2_000_000, 0, 0, 0), "faces": (20_000, 512, 0, 0),
-                "pca": (20_000, 768, 0, 0), "cache": (1_000_000, 768, 0, 0)}[a.workload]
+                "pca": (20_000, 768, 0, 0), "cache": (1_000_000, 768, 0, 0), "i8peak": (8192, 0, 0, 0)}[a.workload]
     a.rows = a.rows or defaults[0]
     a.dim = a.dim or defaults[1]
     a.k = a.k or defaults[2]
     a.queries = a.queries or defaults[3]
     {"scan": run_scan, "gemm": run_gemm, "multi": run_multi, "shared": run_shared, "hamming": run_hamming,
-     "faces": run_faces, "pca": run_pca, "cache": run_cache}[a.workload](a)
+     "faces": run_faces, "pca": run_pca, "cache": run_cache, "i8peak": run_i8peak}[a.workload](a)
 
 
 if __name__ == "__main__":
