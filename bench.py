@@ -353,9 +353,16 @@ def timed_scans(R: Ranks, idx, rq, warm: int, steps: int, k: int):
     return R.max_over_ranks(ms)
 
 
+# int8 x int8 -> int32 tensor rate of this pool's B200 (python -m loki_b200.workloads i8peak: the vendor
+# library's 8192^3 product, best of ten): the denominator for the batched search
+I8_TENSOR_PEAK_TOPS = 3072.0
+
+
 def other_workload(lk, R: Ranks, comm, name: str, total_rows: int, dim: int, store: int, k: int, steps: int, seed: int,
-                   peak: float):
-    """One more shape of the path, its rows split over the ranks (strong scaling of a fixed corpus)."""
+                   peak: float, batch: int = 0):
+    """One more shape of the path, its rows split over the ranks (strong scaling of a fixed corpus).
+    With `batch`, that many queries also go through one lk_search call (host buffers in and out):
+    on an int8 index one tensor-core matrix product per shard and one all-gather for the batch."""
     rows = total_rows // R.world
     base = R.rank * rows
     idx = build_shard(lk, R, rows, dim, store, seed, R.rank)
@@ -374,6 +381,31 @@ def other_workload(lk, R: Ranks, comm, name: str, total_rows: int, dim: int, sto
            "queries": steps, "ms_per_query": per_q * 1e3, "queries_per_s": 1.0 / per_q,
            "hbm_gbs_per_gpu": rows * dim * elem / per_q / 1e9, "hbm_frac_per_gpu": rows * dim * elem / per_q / 1e9 / peak,
            "parity": par}
+    if batch:
+        bq = make_queries(batch, seed + 2000, dim)
+        idx.search(bq[:max(64, batch // 8)], k)          # warm-up: scratch of the batched path
+        R.barrier(idx)
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            got = idx.search(bq, k)
+            dt = R.max_over_ranks(time.perf_counter() - t0)
+            best = dt if best is None else min(best, dt)
+            R.barrier(idx)
+        idx.set_batch_mode(False)                         # the same queries one at a time: must agree bit for bit
+        same = True
+        for qi in (0, batch // 2, batch - 1):
+            one = idx.search_one(bq[qi], k)
+            same &= bool(np.array_equal(one[0][0], got[0][qi]) and np.array_equal(one[2][0], got[2][qi]))
+        idx.set_batch_mode(True)
+        ops = 2.0 * batch * rows * dim
+        out["batch"] = {"queries": batch, "ms_per_call": best * 1e3, "queries_per_s": batch / best,
+                        "int8_tops_per_gpu": ops / best / 1e12, "tensor_frac_per_gpu": ops / best / 1e12 / I8_TENSOR_PEAK_TOPS,
+                        "tensor_peak": f"{I8_TENSOR_PEAK_TOPS:.0f} Tops/s, measured (vendor int8 product, burst)",
+                        "hbm_gbs_per_gpu": rows * dim / best / 1e9, "hbm_frac_per_gpu": rows * dim / best / 1e9 / peak,
+                        "equals_single_scans": same,
+                        "note": "whole call: raw float queries up, quantised on the device, product + fused top-k"
+                                + (", all-gather + merge" if R.world > 1 else "") + ", hits down"}
     rq.close()
     idx.close()
     return name, out
@@ -434,10 +466,14 @@ def run_ours(args):
     peak, peak_kind = load_peaks()
     others = {}
     if not args.no_extras:
-        for spec in (("10,000,000 x 768 int8 over the GPUs of the run, top-10", 10_000_000, 768, lk.LK_I8, 10, 48, 1010),
-                     ("16,000,000 x 1,024 int8 over the GPUs of the run, top-50", 16_000_000, 1024, lk.LK_I8, 50, 32, 1005),
-                     ("100,000 x 512 float32 over the GPUs of the run, top-10", 100_000, 512, lk.LK_F32, 10, 64, 1001)):
-            name, out = other_workload(lk, R, comm, spec[0], spec[1], spec[2], spec[3], spec[4], spec[5], spec[6], peak)
+        for spec in (("10,000,000 x 768 int8 over the GPUs of the run, top-10", 10_000_000, 768, lk.LK_I8, 10, 48, 1010, 0),
+                     ("16,000,000 x 1,024 int8 over the GPUs of the run, top-50; 512 queries also as one batch",
+                      16_000_000, 1024, lk.LK_I8, 50, 32, 1005, 512),
+                     ("2,000,000 x 768 int8 over the GPUs of the run, top-100; 4,096 queries also as one batch",
+                      2_000_000, 768, lk.LK_I8, 100, 16, 1003, 4096),
+                     ("100,000 x 512 float32 over the GPUs of the run, top-10", 100_000, 512, lk.LK_F32, 10, 64, 1001, 0)):
+            name, out = other_workload(lk, R, comm, spec[0], spec[1], spec[2], spec[3], spec[4], spec[5], spec[6], peak,
+                                       batch=spec[7])
             others[name] = out
 
     if rank == 0:

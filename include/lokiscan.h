@@ -171,10 +171,12 @@ LK_API int lk_cosine_sim_topk(const float *rows, int64_t n, int dim, const float
 LK_API int lk_index_save(lk_index *idx, const char *path, uint64_t tag);
 LK_API int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out);
 
-/* How lk_search runs a batch of queries (no allow-list, k <= 256, index not sharded).
+/* How lk_search runs a batch of queries (no allow-list, k <= 256).
  * mode 1 (default): 32 or more queries on an LK_I8 index as one int8 tensor-core matrix
- * product with the top-k fused into its epilogue; 3 or more queries on an LK_F32 index of
- * 8,192+ rows eight to a pass over the corpus on the float64 tensor-core path.
+ * product with the top-k fused into its epilogue (on a sharded index: one such product per
+ * shard, then ONE all-gather of the shards' nq x k ranked hits and a merge on every rank);
+ * 3 or more queries on an unsharded LK_F32 index of 8,192+ rows eight to a pass over the corpus
+ * on the float64 tensor-core path.
  * mode 0: consecutive single-query scans.  int8 results are identical.  float32 scores come
  * from the same arithmetic (exact products, float64 accumulation, one rounding) summed in a
  * different order, so hit lists can differ only between rows whose scores tie to the last bits. */

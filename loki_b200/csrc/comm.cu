@@ -116,6 +116,7 @@ int comm_gather_merge(lk_comm *c, lk_index *idx, const ResultArena &res, int q_f
     m.out_scores = res.d_scores() + o;
     m.out_iscores = res.d_iscores() + o;
     m.out_count = res.d_counts() + q_first;
+    m.out_keys = nullptr;
     LK_TRY(merge_launch(m, idx->stream));
     idx->aux_launches++;
     return 0;

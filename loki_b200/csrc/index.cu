@@ -274,6 +274,7 @@ static int unpack_results(const ResultArena &res, int nq, int k_user, int k_eff,
 // top-k fused into its epilogue (gemm_i8.cu); same scores and ranking as query-by-query scans.
 static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, int k_eff, int64_t *out_ids,
                        float *out_scores, int32_t *out_iscores, int32_t *out_counts) {
+    const bool sharded = idx->comm != nullptr;
     const int slices = gemm_max_slices(idx->sm_count, nq, idx->len);
     const size_t e = (size_t)nq * k_eff;
     // device: queries | query scales | list bases (zeros) | shared thresholds (zeros) | lists [slices][nq][k] | merge scratch
@@ -298,8 +299,9 @@ static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, 
     unsigned long long *d_gthr = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes);
     unsigned long long *d_lists = (unsigned long long *)(dq + q_bytes + qs_bytes + base_bytes + thr_bytes);
     int *d_err = (int *)(idx->d_ticket + 1);
-    LK_TRY(gemm_launch(idx->d_rows, idx->len, idx->ld, dq, nq, k_eff, (unsigned long long *)idx->gemm_cand.p, d_gthr, d_lists,
-                       d_err, idx->sm_count, idx->stream, &idx->aux_launches));
+    if (idx->len > 0)  // an empty shard contributes empty lists
+        LK_TRY(gemm_launch(idx->d_rows, idx->len, idx->ld, dq, nq, k_eff, (unsigned long long *)idx->gemm_cand.p, d_gthr, d_lists,
+                           d_err, idx->sm_count, idx->stream, &idx->aux_launches));
     MergeArgs m;
     m.keys = d_lists;
     m.payload = nullptr;
@@ -315,8 +317,11 @@ static int search_gemm(lk_index *idx, const float *queries, int nq, int k_user, 
     m.out_scores = idx->res.d_scores();
     m.out_iscores = idx->res.d_iscores();
     m.out_count = idx->res.d_counts();
+    m.out_keys = sharded ? idx->res.d_keys() : nullptr;
     LK_TRY(merge_launch(m, idx->stream));
     idx->aux_launches++;
+    // sharded: ONE all-gather of every shard's nq x k ranked keys (+ finished scores), merged on every rank
+    if (sharded) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
     int h_err = 0;
     LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaMemcpyAsync(&h_err, d_err, 4, cudaMemcpyDeviceToHost, idx->stream));
@@ -387,6 +392,7 @@ static int search_multi_f32(lk_index *idx, const float *queries, int nq, int sco
     m.out_scores = idx->res.d_scores();
     m.out_iscores = idx->res.d_iscores();
     m.out_count = idx->res.d_counts();
+    m.out_keys = nullptr;
     LK_TRY(merge_launch(m, idx->stream));
     idx->aux_launches++;
     int h_err = 0;
@@ -701,8 +707,10 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     const int k_eff = sharded ? k : (int)std::min<long long>(k, n_cand);
     const int passes = (k_eff + kMaxK - 1) / kMaxK;
     if (sharded && passes > 1) return fail(LK_ERANGE, "lk_search: k above the single-pass limit is not supported on a sharded index");
-    if (idx->store == LK_I8 && nq >= GEMM_MIN_QUERIES && !filtered && !sharded && gemm_supported(idx->ld, k_eff) &&
-        idx->len >= 4096 && !idx->no_gemm) {
+    // (a sharded index takes the decision from what all ranks share: an empty or small shard must not
+    // send one rank down another path than the others)
+    if (idx->store == LK_I8 && nq >= GEMM_MIN_QUERIES && !filtered && gemm_supported(idx->ld, k_eff) &&
+        (sharded || idx->len >= 4096) && !idx->no_gemm) {
         LK_TRY(search_gemm(idx, queries, nq, k, k_eff, out_ids, out_scores, out_iscores, out_counts));
         idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
         return LK_OK;

@@ -147,6 +147,7 @@ struct MergeArgs {
     float *out_scores;
     int *out_iscores;
     int *out_count;
+    unsigned long long *out_keys;    // nullptr, or [nq][k]: the ranked keys themselves (what a further merge takes)
 };
 int merge_launch(const MergeArgs &a, cudaStream_t stream);
 

@@ -1069,6 +1069,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_merge_lists(const MergeArgs
     const int cnt = buf.ctrl->count;
     for (int i = tid; i < a.k; i += kScanThreads) {
         const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
+        if (a.out_keys) a.out_keys[(size_t)q * a.k + i] = key;
         if (key == 0ull) {
             out_ids[i] = -1;
             out_scores[i] = 0.0f;

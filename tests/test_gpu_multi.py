@@ -48,6 +48,10 @@ for mode in ("nccl", "peer"):
         ids2, scores2, iscores2, counts2 = rq.fetch(0, 5, k)
         assert np.array_equal(ids, ids2) and np.array_equal(scores, scores2) and np.array_equal(iscores, iscores2)
         out[f"{mode}_{name}_ids"], out[f"{mode}_{name}_scores"], out[f"{mode}_{name}_iscores"] = ids, scores, iscores
+        # a batch: int8 runs as one tensor-core product per shard + one all-gather, float32 as queued scans
+        qb = gaussian_rows(70, dim, 8)
+        bi, bs, bisc, _ = idx.search(qb, k)
+        out[f"{mode}_{name}_batch_ids"], out[f"{mode}_{name}_batch_scores"], out[f"{mode}_{name}_batch_iscores"] = bi, bs, bisc
         if mode == "peer":  # k above the peer path's limit falls back to the all-gather
             big = idx.search(queries[:1], 300)
             out[f"big_{name}_ids"] = big[0]
@@ -97,11 +101,16 @@ def test_sharded_search_over_nccl_equals_single_index(lk, tmp_path):
         idx.append(rows)
         ids, scores, iscores, _ = idx.search(queries, k)
         big = idx.search(queries[:1], 300)[0]
+        idx.set_batch_mode(False)
+        bids, bscores, biscores, _ = idx.search(gaussian_rows(70, dim, 8), k)
         for g in got:
             for mode in ("nccl", "peer"):
                 assert np.array_equal(g[f"{mode}_{name}_ids"], ids), (mode, name)
                 assert np.array_equal(g[f"{mode}_{name}_scores"], scores), (mode, name)
                 assert np.array_equal(g[f"{mode}_{name}_iscores"], iscores), (mode, name)
+                assert np.array_equal(g[f"{mode}_{name}_batch_ids"], bids), (mode, name, "batch")
+                assert np.array_equal(g[f"{mode}_{name}_batch_scores"], bscores), (mode, name, "batch")
+                assert np.array_equal(g[f"{mode}_{name}_batch_iscores"], biscores), (mode, name, "batch")
             assert np.array_equal(g[f"big_{name}_ids"], big), name
     from tests.synth import phash_set
     h = phash_set(60000, 21, max_flips=9)
