@@ -157,12 +157,16 @@ __device__ __forceinline__ void g_pair_sync() {
 }
 // 2-D tiled TMA load into THIS CTA's shared memory: box at (x = byte column, y = row) of the tensor
 // map; the bytes are counted on a barrier of the pair's leader (`leader_bar`, from g_leader_addr).
-// Not a multicast load: each CTA of the pair fetches its own half of a tile.
-__device__ __forceinline__ void g_tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, unsigned leader_bar) {
+// Not a multicast load: each CTA of the pair fetches its own half of a tile.  `keep` asks L2 to
+// hold on to the lines (evict-last): a corpus tile is wanted again by the pairs of every other
+// query tile within microseconds, while the candidate keys written meanwhile are not.
+constexpr unsigned long long G_L2_EVICT_NORMAL = 0x1000000000000000ull, G_L2_EVICT_LAST = 0x14F0000000000000ull;
+__device__ __forceinline__ void g_tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, unsigned leader_bar, bool keep) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
             g_smem(dst)),
-        "l"(reinterpret_cast<unsigned long long>(tm)), "r"(x), "r"(y), "r"(leader_bar)
+        "l"(reinterpret_cast<unsigned long long>(tm)), "r"(x), "r"(y), "r"(leader_bar),
+        "l"(keep ? G_L2_EVICT_LAST : G_L2_EVICT_NORMAL)
         : "memory");
 }
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart.
@@ -489,7 +493,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
                 if (rank == 0) g_mbar_expect_tx(&ctl->q_full, (unsigned)(2 * a.ks * GQ_SLICE_BYTES));
                 for (int s = 0; s < a.ks; ++s)
                     g_tma_load_2d(sm_q + (size_t)s * GQ_SLICE_BYTES, &tm_queries, s * GSLICE, sg.qt * 2 * GN + rank * GN,
-                                  q_full_leader);
+                                  q_full_leader, false);
             }
             __syncwarp();
             for (long long t = sg.t0; ok && t < sg.t1; t += sg.stride) {
@@ -499,7 +503,7 @@ k_gemm_i8_topk(const __grid_constant__ CUtensorMap tm_rows, const __grid_constan
                     if (g_elect_one()) {
                         if (rank == 0) g_mbar_expect_tx(&ctl->full[stage], (unsigned)(2 * GSLICE_BYTES));
                         g_tma_load_2d(sm_r + (size_t)stage * GSLICE_BYTES, &tm_rows, s * GSLICE, (int)(t * GM + rank * GR),
-                                      g_leader_addr(g_smem(&ctl->full[stage])));
+                                      g_leader_addr(g_smem(&ctl->full[stage])), true);
                     }
                     __syncwarp();
                     if (++stage == a.stages) {
