@@ -190,6 +190,7 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
     a.cq = cq;
     a.k = k;
     a.bound = nullptr;
+    a.floor = nullptr;
     a.part = (unsigned long long *)idx->part.p;
     a.ticket = idx->d_ticket;
     // consecutive launches may overlap at their edges: each uses its own batch counter and error word
@@ -210,16 +211,83 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
     return a;
 }
 
+// ---------------------------------------------------------------------------
+// Large k: a sampled lower bound for the scan.
+// Every CTA of a scan must keep its own best k rows, because all k best could sit in its
+// part of the corpus; for k = 1,000 on 148 CTAs that is 148,000 keys kept, cut and merged to
+// find 1,000.  Instead, a strided sample of S rows is scanned first (a gathered scan, a few
+// microseconds); the sample's r-th best key becomes an exclusive lower bound for the real
+// scan.  r is chosen so that the expected number of corpus rows above the bound is about
+// 2k and k lies five standard deviations below it: each CTA then keeps a few dozen keys.
+// If fewer than k hits come out after all (a sample that misrepresents the corpus), the
+// caller repeats the scan without the bound, so the result is exact either way.
+// ---------------------------------------------------------------------------
+constexpr int kFloorMinK = 256;       // below this the per-CTA lists are cheap anyway
+constexpr int kSampleMin = 8192, kSampleMax = 65536;
+
+__global__ void k_fill_stride(int *slots, int n, long long len) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        slots[i] = (int)((long long)i * len / n);  // evenly spread over the rows
+}
+
+static bool floor_applies(const lk_index *idx, bool filtered, bool sharded, int k_eff, int passes) {
+    return !idx->no_floor && !filtered && !sharded && passes == 1 && k_eff >= kFloorMinK &&
+           idx->len >= 64ll * k_eff && idx->len >= 4ll * kSampleMin;
+}
+
+// Enqueue the sample scan of one prepared query (in device memory, or inline in `inl`); *floor_out
+// receives the device address of the bound.
+static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const unsigned char *inl, bool centered, float cq,
+                               float qscale, int k_eff, const unsigned long long **floor_out) {
+    const int S = (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 32)) & ~31;
+    const double r = (double)k_eff * S / (double)idx->len;
+    const double x = (5.0 + std::sqrt(25.0 + 4.0 * r)) * 0.5;  // r' - 5 sqrt(r') >= r
+    const int rr = std::min<int>(kMaxK, std::max<int>(16, (int)std::ceil(x * x)));
+    if (idx->plan_sample_k != rr) {
+        LK_TRY(scan_plan(idx->type, idx->chunks, rr, idx->device, &idx->plan_sample));
+        idx->plan_sample_k = rr;
+    }
+    // slots [S] | keys [rr] | ids [rr] | scores [rr] | iscores [rr] | count
+    const size_t o_keys = (size_t)round_up((int64_t)S * 4, 256), o_ids = o_keys + (size_t)rr * 8, o_sc = o_ids + (size_t)rr * 8;
+    const size_t o_isc = o_sc + (size_t)rr * 4, o_cnt = o_isc + (size_t)rr * 4;
+    const void *before = idx->d_sample.p;
+    LK_TRY(idx->d_sample.reserve(o_cnt + 16));
+    if (idx->d_sample.p != before || idx->sample_len != idx->len || idx->sample_n != S) {
+        k_fill_stride<<<64, 256, 0, idx->stream>>>((int *)idx->d_sample.p, S, idx->len);
+        LK_CUDA(cudaGetLastError());
+        idx->sample_len = idx->len;
+        idx->sample_n = S;
+        idx->aux_launches++;
+    }
+    LK_TRY(idx->part.reserve((size_t)scan_max_grid(idx->plan_sample) * rr * 8));
+    unsigned char *b = (unsigned char *)idx->d_sample.p;
+    ScanArgs a = base_args(idx, centered, cq, qscale, (const int *)b, S, rr);
+    a.query = d_q;
+    if (d_q == nullptr) memcpy(a.query_inline, inl, (size_t)idx->qbytes);
+    a.out_keys = (unsigned long long *)(b + o_keys);
+    a.out_ids = (long long *)(b + o_ids);
+    a.out_scores = (float *)(b + o_sc);
+    a.out_iscores = (int *)(b + o_isc);
+    a.out_count = (int *)(b + o_cnt);
+    LK_TRY(scan_launch(idx->type, a, idx->plan_sample, idx->stream, false));
+    idx->scan_launches++;
+    *floor_out = (const unsigned long long *)(b + o_keys) + (rr - 1);
+    return 0;
+}
+
 // Enqueue the scan(s) of one prepared query.  k_eff hits are selected in passes of
 // at most kMaxK; pass p accepts only keys below the last key of pass p-1.
 static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered, float cq, float qscale,
                          const int *d_slots, long long n_cand, int k_eff, int k_stride, int passes,
                          const ResultArena &res, int qi, const PeerTable *peer = nullptr, unsigned int seq = 0,
-                         int batch_pos = 0) {
+                         int batch_pos = 0, bool use_floor = false) {
+    const unsigned long long *floor = nullptr;
+    if (use_floor) LK_TRY(enqueue_sample_scan(idx, d_q, nullptr, centered, cq, qscale, k_eff, &floor));
     for (int p = 0; p < passes; ++p) {
         const int done = p * kMaxK;
         ScanArgs a = base_args(idx, centered, cq, qscale, d_slots, n_cand, std::min(kMaxK, k_eff - done));
         a.query = d_q;
+        a.floor = floor;
         const size_t o = (size_t)qi * k_stride + done;
         a.bound = (p == 0) ? nullptr : res.d_keys() + o - 1;
         a.out_keys = res.d_keys() + o;
@@ -424,6 +492,11 @@ static int search_one_fast(lk_index *idx, const float *query, int scoring, const
     float cq = 0.0f, qscale = 0.0f;
     ScanArgs a = base_args(idx, false, 0.0f, 0.0f, d_slots, n_cand, k_eff);
     const bool centered = prepare_query(idx, query, scoring, a.query_inline, &cq, &qscale);
+    const bool use_floor = floor_applies(idx, d_slots != nullptr, peer != nullptr || idx->comm != nullptr, k_eff, 1);
+    if (use_floor) {
+        LK_TRY(enqueue_sample_scan(idx, nullptr, a.query_inline, centered, cq, qscale, k_eff, &a.floor));
+        a.part = (unsigned long long *)idx->part.p;  // the sample scan may have grown the scratch
+    }
     a.cnorm = centered ? idx->d_cnorm : nullptr;
     a.cq = cq;
     a.qscale = qscale;
@@ -451,6 +524,13 @@ static int search_one_fast(lk_index *idx, const float *query, int scoring, const
     std::atomic_thread_fence(std::memory_order_acquire);
     int cnt = *(volatile int *)(z + off_count);
     if (cnt < 0) return fail(LK_ETIMEOUT, "a scan kernel gave up on a bounded wait (bulk copy or another rank); results are not valid");
+    if (use_floor && cnt < k_eff) {  // the sampled bound was too high for this corpus: once more without it
+        idx->no_floor = true;
+        const int st = search_one_fast(idx, query, scoring, d_slots, n_cand, k_eff, peer, k_user, out_ids, out_scores, out_iscores,
+                                       out_counts);
+        idx->no_floor = false;
+        return st;
+    }
     if (cnt > k_eff) cnt = k_eff;
     const long long *ids = (const long long *)z;
     const float *sc = (const float *)(z + off_scores);
@@ -576,6 +656,7 @@ int lk_index_destroy(lk_index *idx) {
     idx->h_query.release();
     idx->zc.release();
     idx->gemm_cand.release();
+    idx->d_sample.release();
     idx->gather.release();
     if (idx->ev0) cudaEventDestroy(idx->ev0);
     if (idx->ev1) cudaEventDestroy(idx->ev1);
@@ -754,16 +835,30 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     }
     // sharded: exchange inside the scan kernel over peer memory when that is set up, else NCCL
     unsigned int seq = 0;
+    const bool use_floor = floor_applies(idx, filtered, sharded, k_eff, passes);
     for (int q = 0; q < nq; ++q) {
         seq = peer ? comm_next_seq(idx->comm) : 0u;
         LK_TRY(enqueue_query(idx, (const unsigned char *)idx->d_query.p + (size_t)q * idx->qbytes, cen[q] != 0, cq[q],
-                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer, seq, q));
+                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer, seq, q, use_floor));
     }
     if (peer) LK_TRY(drain_queued(idx, peer, idx->res, nq - 1, seq, nq, k_eff));
     if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
     LK_CUDA(cudaMemcpyAsync(idx->res.host.p, idx->res.dev.p, idx->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
     LK_TRY(unpack_results(idx->res, nq, k, k_eff, passes, out_ids, out_scores, out_iscores, out_counts));
+    if (use_floor) {  // a query whose sampled bound turned out too high: once more, alone and without it
+        std::vector<int32_t> counts((size_t)nq);
+        for (int q = 0; q < nq; ++q) counts[q] = idx->res.h_counts()[q];
+        for (int q = 0; q < nq; ++q) {
+            if (counts[q] >= k_eff) continue;
+            idx->no_floor = true;
+            const int st = lk_search(idx, queries + (size_t)q * idx->dim, 1, k, scoring, nullptr, 0, out_ids ? out_ids + (size_t)q * k : nullptr,
+                                     out_scores ? out_scores + (size_t)q * k : nullptr,
+                                     out_iscores ? out_iscores + (size_t)q * k : nullptr, out_counts ? out_counts + q : nullptr);
+            idx->no_floor = false;
+            LK_TRY(st);
+        }
+    }
     idx->last_search_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return LK_OK;
 }

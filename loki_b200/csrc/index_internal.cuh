@@ -131,6 +131,13 @@ struct lk_index {
     lk::PinnedBuf h_query;
     lk::PinnedBuf zc;           // mapped pinned block the kernel writes single-query results into
     unsigned int zc_seq = 0;
+    // large-k searches: a strided sample of the rows is scanned first and gives the scan a lower bound
+    lk::DevBuf d_sample;        // sample slot numbers | sample scan's outputs (keys, ids, scores, count)
+    long long sample_len = -1;  // index length the slot numbers were made for
+    int sample_n = 0;
+    lk::ScanPlan plan_sample;
+    int plan_sample_k = -1;
+    bool no_floor = false;      // set while a search is repeated without the bound
     lk::DevBuf gemm_cand;       // candidate lists of the batched tensor-core search
     bool no_gemm = false;       // batches run as single-query scans (lk_index_set_batch_mode)
     // multi-GPU

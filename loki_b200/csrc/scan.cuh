@@ -37,6 +37,11 @@ struct ScanArgs {
     float cq;                   // <qc, mu> of the centered query
     int k;                      // 1..kMaxK
     const unsigned long long *bound;  // nullptr, or exclusive upper bound on accepted keys
+    // nullptr, or an exclusive LOWER bound: keys at or below *floor are not candidates.  For large k the
+    // caller first scans a sample of the rows and takes a key that, with a wide margin, at least k rows
+    // of the whole corpus exceed: each CTA then keeps a few dozen candidates instead of its own best k.
+    // Should fewer than k hits come out after all, the caller repeats the scan without a floor.
+    const unsigned long long *floor;
     unsigned long long *part;   // scratch [grid][k]: per-CTA candidate lists
     unsigned int *ticket;       // scratch: CTAs finished so far (self-resetting)
     unsigned int *next_batch;   // scratch: next 32-row batch to hand out (TMA-staged kernel; self-resetting)

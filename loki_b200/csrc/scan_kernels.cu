@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) k_scan(const __grid_constant_
     if (tid == 0) {
         buf.ctrl->count = 0;
         buf.ctrl->n_done = 0;
-        buf.ctrl->thr = 0ull;
+        buf.ctrl->thr = a.floor ? __ldcg(a.floor) : 0ull;
     }
     TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
     const unsigned long long bound = a.bound ? __ldcg(a.bound) : ~0ull;
@@ -642,9 +642,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
     }
     TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
     unsigned long long bound = ~0ull;
-    if (a.bound != nullptr) {  // a later pass of a large-k search: its bound is the previous pass's output
+    if (a.bound != nullptr || a.floor != nullptr) {
+        // a later pass of a large-k search (its bound is the previous pass's output) or a search with a
+        // sampled floor (the output of the sample scan launched just before): wait for that launch
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        bound = __ldcg(a.bound);
+        if (a.bound != nullptr) bound = __ldcg(a.bound);
+        if (a.floor != nullptr && tid == 0) buf.ctrl->thr = __ldcg(a.floor);
     }
     __syncthreads();
 
@@ -854,9 +857,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
     }
     TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
     unsigned long long bound = ~0ull;
-    if (a.bound != nullptr) {
+    if (a.bound != nullptr || a.floor != nullptr) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        bound = __ldcg(a.bound);
+        if (a.bound != nullptr) bound = __ldcg(a.bound);
+        if (a.floor != nullptr && tid == 0) buf.ctrl->thr = __ldcg(a.floor);
     }
     __syncthreads();
     typename TR::QChunk q[NJ];

@@ -196,3 +196,59 @@ def test_queued_scans_on_narrow_rows(lk, store, dim, n):
                 assert abs(sc[ids[q, i]] - wsc[i]) <= tol * max(abs(wsc[i]), 1e-6)
     rq.close()
     idx.close()
+
+
+@pytest.mark.parametrize("store,n,dim,k", [("i8", 600_000, 768, 1000), ("i8", 600_000, 768, 2048), ("f32", 300_000, 512, 500),
+                                           ("i8", 400_000, 1024, 256)])
+def test_large_k_scan_with_sampled_bound(lk, store, n, dim, k):
+    """k of 256 and more on a large index: a strided sample of the rows is scanned first and bounds
+    the scan from below, so that a CTA keeps a few dozen candidates instead of its own best k.
+    The hit list must be the oracle's all the same."""
+    st = lk.LK_I8 if store == "i8" else lk.LK_F32
+    idx, _, _ = device_corpus(lk, n, dim, st, 77 + k)
+    queries = gaussian_rows(3, dim, 78 + k)
+    if store == "i8":
+        codes, _ = idx.read_rows()
+        both = idx.search(queries[:2], k)                     # two queries in one call
+        for q in range(3):
+            wid, wsc = _oracle_hits_i8(codes, queries[q], k)
+            ids, _, isc, cnt = idx.search(queries[q], k)      # one synchronous call
+            assert cnt[0] == k and np.array_equal(ids[0], wid) and np.array_equal(isc[0], wsc), f"query {q}"
+            if q < 2:
+                assert np.array_equal(both[0][q], wid) and np.array_equal(both[2][q], wsc)
+    else:
+        idx.set_batch_mode(False)
+        rows = idx.read_rows()
+        for q in range(3):
+            sc = O.scan_f32(rows, O.normalize(queries[q]), workers=CORES)
+            got = idx.search(queries[q], k)
+            assert got[3][0] == k
+            _assert_f32_hits(got[0][0], got[1][0], sc, k)
+    idx.close()
+
+
+def test_large_k_scan_when_the_sample_misleads(lk):
+    """Every row the sample looks at is a near-copy of the query and no other row is: the bound taken from
+    the sample lies above almost the whole corpus, fewer than k rows pass, and the search must notice
+    and run again without the bound."""
+    n, dim, k = 524_288, 64, 400
+    rows = gaussian_rows(n, dim, 5150)
+    q = gaussian_rows(1, dim, 5151)[0]
+    stride = 32                                   # the sample takes every 32nd row of an index of this size
+    rng = np.random.default_rng(5)
+    rows[::stride] = q + 0.05 * rng.standard_normal((n // stride, dim)).astype(np.float32)
+    for store in (lk.LK_I8, lk.LK_F32):
+        idx = lk.DeviceIndex(dim, store)
+        idx.append(rows)
+        idx.set_batch_mode(False)
+        if store == lk.LK_I8:
+            codes, _ = idx.read_rows()
+            wid, wsc = _oracle_hits_i8(codes, q, k)
+            ids, _, isc, cnt = idx.search(q, k)
+            assert cnt[0] == k and np.array_equal(ids[0], wid) and np.array_equal(isc[0], wsc)
+        else:
+            sc = O.scan_f32(idx.read_rows(), O.normalize(q), workers=CORES)
+            got = idx.search(q, k)
+            assert got[3][0] == k
+            _assert_f32_hits(got[0][0], got[1][0], sc, k)
+        idx.close()
