@@ -164,13 +164,16 @@ static bool prepare_query(const lk_index *idx, const float *q, int scoring, unsi
     return false;
 }
 
+// the per-CTA list lengths live in the last bytes of the list scratch (room for 2,048 CTAs)
+constexpr size_t kPartCntBytes = 8192;
+
 static int ensure_scan_scratch(lk_index *idx, int k) {
     if (idx->grid_for_k != k) {
         LK_TRY(scan_plan(idx->type, idx->chunks, k, idx->device, &idx->plan));
         idx->grid = scan_max_grid(idx->plan);
         idx->grid_for_k = k;
     }
-    LK_TRY(idx->part.reserve((size_t)idx->grid * k * 8));
+    LK_TRY(idx->part.reserve((size_t)idx->grid * k * 8 + kPartCntBytes));
     return 0;
 }
 
@@ -192,6 +195,7 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
     a.bound = nullptr;
     a.floor = nullptr;
     a.part = (unsigned long long *)idx->part.p;
+    a.part_cnt = idx->part.p ? (int *)((unsigned char *)idx->part.p + idx->part.bytes - kPartCntBytes) : nullptr;
     a.ticket = idx->d_ticket;
     // consecutive launches may overlap at their edges: each uses its own batch counter and error word
     a.error = (int *)(idx->d_ticket + 8 + (idx->scan_launches % kScanOverlap));
@@ -259,7 +263,7 @@ static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const un
         idx->sample_n = S;
         idx->aux_launches++;
     }
-    LK_TRY(idx->part.reserve((size_t)scan_max_grid(idx->plan_sample) * rr * 8));
+    LK_TRY(idx->part.reserve((size_t)scan_max_grid(idx->plan_sample) * rr * 8 + kPartCntBytes));
     unsigned char *b = (unsigned char *)idx->d_sample.p;
     ScanArgs a = base_args(idx, centered, cq, qscale, (const int *)b, S, rr);
     a.query = d_q;
@@ -496,6 +500,7 @@ static int search_one_fast(lk_index *idx, const float *query, int scoring, const
     if (use_floor) {
         LK_TRY(enqueue_sample_scan(idx, nullptr, a.query_inline, centered, cq, qscale, k_eff, &a.floor));
         a.part = (unsigned long long *)idx->part.p;  // the sample scan may have grown the scratch
+        a.part_cnt = (int *)((unsigned char *)idx->part.p + idx->part.bytes - kPartCntBytes);
     }
     a.cnorm = centered ? idx->d_cnorm : nullptr;
     a.cq = cq;

@@ -63,6 +63,18 @@ __device__ __forceinline__ uint32_t lanemask_lt() {
     asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
     return m;
 }
+__device__ __forceinline__ uint64_t shfl_u64(uint64_t v, int src_lane) {
+    uint32_t lo = (uint32_t)v, hi = (uint32_t)(v >> 32);
+    lo = __shfl_sync(0xffffffffu, lo, src_lane);
+    hi = __shfl_sync(0xffffffffu, hi, src_lane);
+    return ((uint64_t)hi << 32) | lo;
+}
+__device__ __forceinline__ uint64_t shfl_up_u64(uint64_t v, int delta) {
+    uint32_t lo = (uint32_t)v, hi = (uint32_t)(v >> 32);
+    lo = __shfl_up_sync(0xffffffffu, lo, delta);
+    hi = __shfl_up_sync(0xffffffffu, hi, delta);
+    return ((uint64_t)hi << 32) | lo;
+}
 __device__ __forceinline__ uint64_t shfl_xor_u64(uint64_t v, int m) {
     uint32_t lo = (uint32_t)v, hi = (uint32_t)(v >> 32);
     lo = __shfl_xor_sync(0xffffffffu, lo, m);

@@ -43,6 +43,7 @@ struct ScanArgs {
     // Should fewer than k hits come out after all, the caller repeats the scan without a floor.
     const unsigned long long *floor;
     unsigned long long *part;   // scratch [grid][k]: per-CTA candidate lists
+    int *part_cnt;              // scratch [grid]: keys in each of them (nullptr: not recorded; the merge then searches)
     unsigned int *ticket;       // scratch: CTAs finished so far (self-resetting)
     unsigned int *next_batch;   // scratch: next 32-row batch to hand out (TMA-staged kernel; self-resetting)
     int *error;                 // scratch: raised by a CTA whose bounded wait ran out (self-resetting)

@@ -345,13 +345,14 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
     const int tid = threadIdx.x, T = blockDim.x;
     unsigned long long *mine = a.part + (size_t)blockIdx.x * a.k;
     for (int i = tid; i < a.k; i += T) mine[i] = buf.keys[i];
+    if (tid == 0 && a.part_cnt != nullptr) a.part_cnt[blockIdx.x] = min(buf.ctrl->count, a.k);
     __threadfence();
     __syncthreads();
     if (tid == 0) *s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
     __syncthreads();
     if (!*s_last) return;
     __threadfence();
-    cand_select_from_lists(buf, a.part, (int)gridDim.x);
+    if (!cand_select_flat(buf, a.part, a.part_cnt, (int)gridDim.x)) cand_select_from_lists(buf, a.part, (int)gridDim.x);
     int cnt = buf.ctrl->count;
     // a CTA whose bounded wait ran out has raised the flag before publishing its list
     const bool scan_bad = a.error != nullptr && *(volatile int *)a.error != 0;
@@ -402,10 +403,9 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
             count_to = nullptr;  // merged later, by a following launch or the drain
         }
     }
-    if (a.done_flag != nullptr) {  // results may sit in host memory: make them visible there first
-        __threadfence_system();
-        __syncthreads();
-    }
+    // results may sit in host memory: all threads' writes are ordered before thread 0's system-scope
+    // fence below by this barrier (one fence for the CTA, not one per thread)
+    if (a.done_flag != nullptr) __syncthreads();
     if (tid == 0) {
         if (count_to != nullptr) *count_to = cnt;
         if (a.error != nullptr) *a.error = 0;
@@ -660,6 +660,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
 
     long long m = 0;
     bool counted = false, failed = false;
+    // small k without a bound: the warp keeps its best keys in registers (warp_top_offer)
+    const bool regk = a.k <= 32 && a.bound == nullptr && a.floor == nullptr;
+    unsigned long long wk = 0ull, wthr = 0ull;
     acc_t acc[G];
     for (;;) {
         const int s = (int)(m % kBulkStages);
@@ -720,10 +723,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
             const unsigned slot = (unsigned)(row0 + lane);
             unsigned long long key = 0ull;
             if (valid) key = make_key(TR::finish(total, a, slot), slot);
-            const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
-            cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            if (regk) {
+                warp_top_offer(wk, wthr, a.k, valid && key > wthr, key, lane);
+            } else {
+                const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
+                cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            }
             continue;
         }
+        if (regk && !work && !counted) cand_offer_warp(buf, lane < a.k && wk != 0ull, wk);  // hand the warp's list over, once
         if (cand_rendezvous(buf, work, counted, lane, WARPS)) break;
     }
     // A warp that gave up may still have copies in flight into its stages: wait for
@@ -869,6 +877,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
 
     long long m = 0;
     bool counted = false, failed = false;
+    // small k without a bound: the warp keeps its best keys in registers (warp_top_offer)
+    const bool regk = a.k <= 32 && a.bound == nullptr && a.floor == nullptr;
+    unsigned long long wk = 0ull, wthr = 0ull;
     for (;;) {
         const int s = (int)(m % kBulkStages);
         long long b = -1;
@@ -911,10 +922,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
             const unsigned slot = (unsigned)row;
             unsigned long long key = 0ull;
             if (valid) key = make_key(TR::finish(total, a, slot), slot);
-            const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
-            cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            if (regk) {
+                warp_top_offer(wk, wthr, a.k, valid && key > wthr, key, lane);
+            } else {
+                const unsigned long long thr = *(volatile unsigned long long *)&buf.ctrl->thr;
+                cand_offer_warp(buf, valid && key > thr && key < bound, key);
+            }
             continue;
         }
+        if (regk && !work && !counted) cand_offer_warp(buf, lane < a.k && wk != 0ull, wk);  // hand the warp's list over, once
         if (cand_rendezvous(buf, work, counted, lane, WARPS)) break;
     }
     if (failed) {
@@ -1220,6 +1236,19 @@ static wide_fn pick_wide(int type, int nj) {
     }
 }
 
+// The dynamic shared-memory limit of a kernel is process-wide state and plans for several k coexist
+// (a sample scan with a small k beside the scan proper): the limit is always raised to the most a CTA
+// of that kernel may have, never to what one plan needs.
+static cudaError_t raise_smem_limit(const void *fn, int device) {
+    int optin = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (e != cudaSuccess) return e;
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, fn);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - (int)fa.sharedSizeBytes);
+}
+
 int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
     ScanPlan p;
     int sms = 0;
@@ -1232,7 +1261,7 @@ int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
     p.smem = head + q;
     {
         scan_fn fn = pick(type, p.g);
-        e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        e = raise_smem_limit((const void *)fn, device);
         int per_sm = 0;
         if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void *)fn, kScanThreads, p.smem);
         if (e != cudaSuccess) return fail(4, std::string("scan plan: ") + cudaGetErrorString(e));
@@ -1263,8 +1292,7 @@ int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
                       (size_t)p.wide_warps * kBulkStages * stage;
         p.wide_run = (int)std::max<size_t>(1, (size_t)24576 / stage);
         if (p.wide_smem <= kSmemLimit) {
-            e = cudaFuncSetAttribute((const void *)pick_wide(type, p.wide_nj),
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.wide_smem);
+            e = raise_smem_limit((const void *)pick_wide(type, p.wide_nj), device);
             if (e != cudaSuccess) return fail(4, std::string("scan plan (wide): ") + cudaGetErrorString(e));
             p.wide_ok = true;
             e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&p.wide_per_sm, (const void *)pick_wide(type, p.wide_nj),
@@ -1274,7 +1302,7 @@ int scan_plan(int type, int chunks, int k, int device, ScanPlan *plan) {
     }
     if (p.bulk_ok) {
         bulk_fn fn = pick_bulk(type, p);
-        e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.bulk_smem);
+        e = raise_smem_limit((const void *)fn, device);
         if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&p.bulk_per_sm, (const void *)fn, kBulkWarps * 32, p.bulk_smem);
         if (e != cudaSuccess) return fail(4, std::string("scan plan (bulk): ") + cudaGetErrorString(e));
     }

@@ -48,6 +48,32 @@ struct CandBuf {
 __device__ inline void cand_prune(const CandBuf &b) {
     const int tid = threadIdx.x, T = blockDim.x;
     const int c = b.ctrl->count;
+    if (c <= 32) {
+        // few keys: one warp sorts them in registers (a bitonic network over the lanes), no barriers
+        if (tid < 32) {
+            unsigned long long v = (tid < c) ? b.keys[tid] : 0ull;
+#pragma unroll
+            for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+                for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                    const unsigned long long o = shfl_xor_u64(v, stride);
+                    const bool lower = (tid & stride) == 0;
+                    const bool desc = (tid & size) == 0;
+                    v = ((v > o) == (lower == desc)) ? v : o;  // the lower lane of a descending pair keeps the larger key
+                }
+            }
+            const int keep = c < b.k ? c : b.k;
+            b.keys[tid] = (tid < keep) ? v : 0ull;
+            // the k-th key (lane k-1, when there are k) raises the threshold
+            const unsigned long long kth = shfl_u64(v, (b.k - 1) & 31);
+            if (tid == 0) {
+                b.ctrl->count = keep;
+                if (keep == b.k && kth > b.ctrl->thr) b.ctrl->thr = kth;  // only ever rises
+            }
+        }
+        __syncthreads();
+        return;
+    }
     int sz = 2;
     while (sz < c) sz <<= 1;
     for (int i = c + tid; i < sz; i += T) b.keys[i] = 0ull;
@@ -87,6 +113,55 @@ __device__ __forceinline__ void cand_offer_warp(const CandBuf &b, bool pass, uns
     if (lane == leader) base = atomicAdd(&b.ctrl->count, __popc(m));
     base = __shfl_sync(0xffffffffu, base, leader);
     if (pass) b.keys[base + __popc(m & lanemask_lt())] = key;
+}
+
+// ---------------------------------------------------------------------------
+// Small k (<= 32): a warp keeps its own best keys in registers, lane i holding the i-th best
+// (descending, 0 = none yet), and never touches the CTA's buffer or a barrier while it streams:
+// the buffer's prune is a meeting of all warps, during which none of them has copies in flight.
+// A batch's candidates are inserted one by one (a ballot gives the place, a shuffle makes room)
+// when they are few, or sorted and merged as a whole (bitonic networks over the lanes) when many
+// pass, as in the first batches.  `wthr` is the key at lane k-1, the warp's own threshold.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void warp_top_offer(unsigned long long &wk, unsigned long long &wthr, int k, bool pass,
+                                               unsigned long long key, int lane) {
+    unsigned m = __ballot_sync(0xffffffffu, pass);
+    if (m == 0u) return;
+    if (__popc(m) <= 4) {
+        while (m != 0u) {  // warp-uniform
+            const int src = __ffs(m) - 1;
+            m &= m - 1u;
+            const unsigned long long c = shfl_u64(key, src);
+            if (c <= wthr) continue;  // an earlier insertion of this batch may have raised the threshold
+            const int pos = __popc(__ballot_sync(0xffffffffu, wk > c));  // wk is descending: the lanes above c are a prefix
+            const unsigned long long up = shfl_up_u64(wk, 1);
+            wk = lane < pos ? wk : (lane == pos ? c : up);
+            wthr = shfl_u64(wk, k - 1);
+        }
+        return;
+    }
+    unsigned long long c = pass ? key : 0ull;
+#pragma unroll
+    for (int size = 2; size <= 32; size <<= 1) {  // sort the candidates, descending over the lanes
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const unsigned long long o = shfl_xor_u64(c, stride);
+            const bool lower = (lane & stride) == 0, desc = (lane & size) == 0;
+            c = ((c > o) == (lower == desc)) ? c : o;
+        }
+    }
+    // best 32 of two descending runs: pair the i-th of one with the (31-i)-th of the other, keep the
+    // larger (a bitonic sequence), then five merge steps
+    const unsigned long long r = shfl_u64(c, 31 - lane);
+    unsigned long long v = wk > r ? wk : r;
+#pragma unroll
+    for (int stride = 16; stride > 0; stride >>= 1) {
+        const unsigned long long o = shfl_xor_u64(v, stride);
+        const bool lower = (lane & stride) == 0;
+        v = ((v > o) == lower) ? v : o;
+    }
+    wk = v;
+    wthr = shfl_u64(wk, k - 1);
 }
 
 // Select the best k out of `lists` ranked lists of k keys each (global memory, zero
@@ -212,6 +287,77 @@ __device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned l
         }
     }
     cand_prune(b);
+}
+
+// The same selection without bisection, for when every list's length is known (cnts[l] keys, then
+// zeros).  One round trip fetches every list's entry at position p (for the starting threshold, as
+// above) together with the lengths; then one thread per list walks its list from the top in chunks
+// of eight independent loads and keeps what beats the threshold, stopping at the first key that
+// does not: the lists are ranked, so that is a prefix, usually inside the first chunk.  Returns
+// false when more keys survive than the buffer holds (the caller then runs
+// cand_select_from_lists, which starts over).  All threads of the CTA call this in lockstep.
+__device__ inline bool cand_select_flat(const CandBuf &b, const unsigned long long *src, const int *cnts, int lists,
+                                        int stride = 0) {
+    const int tid = threadIdx.x, T = blockDim.x;
+    if (stride == 0) stride = b.k;
+    if (cnts == nullptr || lists > b.cap) return false;
+    __shared__ int s_over;
+    for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
+    if (tid == 0) {
+        b.ctrl->count = 0;
+        b.ctrl->thr = 0ull;
+        s_over = 0;
+    }
+    __syncthreads();
+    const int p = (b.k + lists - 1) / lists - 1;
+    const int j = (b.k + p) / (p + 1);
+    for (int l = tid; l < lists; l += T) b.keys[l] = __ldcg(src + (size_t)l * stride + p);
+    __syncthreads();
+    for (int l = tid; l < lists; l += T) {
+        const unsigned long long h = b.keys[l];
+        int r0 = 0, r1 = 0, r2 = 0, r3 = 0;  // independent counts: the shared-memory reads overlap
+        int m = 0;
+        for (; m + 4 <= lists; m += 4) {
+            r0 += (b.keys[m] > h) ? 1 : 0;
+            r1 += (b.keys[m + 1] > h) ? 1 : 0;
+            r2 += (b.keys[m + 2] > h) ? 1 : 0;
+            r3 += (b.keys[m + 3] > h) ? 1 : 0;
+        }
+        for (; m < lists; ++m) r0 += (b.keys[m] > h) ? 1 : 0;
+        const int rank = r0 + r1 + r2 + r3;
+        if (rank == j - 1 && h > 0ull) b.ctrl->thr = h - 1ull;  // keys are unique: one writer
+    }
+    __syncthreads();
+    for (int l = tid; l < lists; l += T) b.keys[l] = 0ull;
+    __syncthreads();
+    const unsigned long long thr0 = b.ctrl->thr;
+    for (int l = tid; l < lists; l += T) {
+        const unsigned long long *lst = src + (size_t)l * stride;
+        const int c = min(__ldcg(cnts + l), b.k);  // (entries past the length are zero: the bound below is b.k,
+        for (int base = 0; base < c; base += 8) {  //  so that the loads need not wait for the length)
+            unsigned long long key[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) key[u] = (base + u < b.k) ? __ldcg(lst + base + u) : 0ull;
+            int take = 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) take += (key[u] > thr0) ? 1 : 0;  // ranked: the takers come first
+            if (take > 0) {
+                const int at = atomicAdd(&b.ctrl->count, take);
+                if (at + take <= b.cap) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (u < take) b.keys[at + u] = key[u];
+                } else {
+                    s_over = 1;
+                }
+            }
+            if (take < 8) break;
+        }
+    }
+    __syncthreads();
+    if (s_over != 0) return false;
+    cand_prune(b);
+    return true;
 }
 
 }  // namespace lk
