@@ -352,7 +352,10 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
     __syncthreads();
     if (!*s_last) return;
     __threadfence();
-    if (!cand_select_flat(buf, a.part, a.part_cnt, (int)gridDim.x)) cand_select_from_lists(buf, a.part, (int)gridDim.x);
+    if (a.k <= 32 && (int)(blockDim.x >> 5) * 32 <= buf.cap)
+        cand_select_small(buf, a.part, (int)gridDim.x);
+    else if (!cand_select_flat(buf, a.part, a.part_cnt, (int)gridDim.x))
+        cand_select_from_lists(buf, a.part, (int)gridDim.x);
     int cnt = buf.ctrl->count;
     // a CTA whose bounded wait ran out has raised the flag before publishing its list
     const bool scan_bad = a.error != nullptr && *(volatile int *)a.error != 0;

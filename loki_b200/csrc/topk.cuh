@@ -289,6 +289,60 @@ __device__ inline void cand_select_from_lists(const CandBuf &b, const unsigned l
     cand_prune(b);
 }
 
+// The selection for small k (<= 32): no starting threshold to work out and no list lengths needed.
+// One thread per list fetches the list's head chunk (one round trip for all lists); every warp then
+// folds its 32 lists into a register-held best-k with warp_top_offer, position by position, and stops
+// as soon as no lane's next key beats the warp's threshold (the lists are ranked, so nothing further
+// down can); the warps' lists meet in the buffer for one small sort.  All threads of the CTA call this
+// in lockstep.
+__device__ inline void cand_select_small(const CandBuf &b, const unsigned long long *src, int lists, int stride = 0) {
+    const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31;
+    if (stride == 0) stride = b.k;
+    for (int i = tid; i < b.cap; i += T) b.keys[i] = 0ull;
+    if (tid == 0) {
+        b.ctrl->count = 0;
+        b.ctrl->thr = 0ull;
+    }
+    __syncthreads();
+    unsigned long long wk = 0ull, wthr = 0ull;
+    for (int l0 = 0; l0 < lists; l0 += T) {  // the same trip count for every thread
+        const int l = l0 + tid;
+        const unsigned long long *lst = src + (size_t)min(l, lists - 1) * stride;
+        for (int base = 0; base < b.k; base += 8) {
+            unsigned long long key[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) key[u] = (l < lists && base + u < b.k) ? __ldcg(lst + base + u) : 0ull;
+            bool more = false;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                warp_top_offer(wk, wthr, b.k, key[u] > wthr, key[u], lane);
+                more = key[u] > wthr;  // after the offer: does this list still reach into the warp's best k?
+            }
+            if (!__any_sync(0xffffffffu, more)) break;
+        }
+    }
+    // the warps' lists meet in the buffer (warp w at [32w, 32w+32)); warp 0 folds them into its own
+    const int warp = tid >> 5, nwarps = T >> 5;
+    b.keys[warp * 32 + lane] = wk;
+    __syncthreads();
+    if (warp == 0) {
+        for (int w = 1; w < nwarps; ++w) {
+            const unsigned long long c = b.keys[w * 32 + lane];
+            warp_top_offer(wk, wthr, b.k, c > wthr, c, lane);
+        }
+        const bool keep = lane < b.k && wk != 0ull;
+        b.keys[lane] = keep ? wk : 0ull;
+        const int cnt = __popc(__ballot_sync(0xffffffffu, keep));
+        if (lane == 0) {
+            b.ctrl->count = cnt;
+            if (cnt == b.k) b.ctrl->thr = wthr;
+        }
+    }
+    __syncthreads();
+    for (int i = 32 + tid; i < nwarps * 32; i += T) b.keys[i] = 0ull;
+    __syncthreads();
+}
+
 // The same selection without bisection, for when every list's length is known (cnts[l] keys, then
 // zeros).  One round trip fetches every list's entry at position p (for the starting threshold, as
 // above) together with the lengths; then one thread per list walks its list from the top in chunks
