@@ -13,7 +13,14 @@
 #include "../../include/lokiscan_index.h"
 #include "lk_common.cuh"
 
+namespace lk {  // index.cu
+int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum);
+uint64_t cache_hash(const void *p, size_t n, uint64_t seed);
+}  // namespace lk
+
 using lk::fail;
+using lk::cache_identity;
+using lk::cache_hash;
 
 struct lkx_index {
     int centered = 0, store = 0, device = 0;
@@ -266,20 +273,37 @@ void lkx_hits_free(lkx_hits *h) { delete h; }
 
 // ---- on-disk cache: the device-side file of lk_index_save plus the paths in slot order ----
 
+// `<path>.paths`: a 40-byte header (magic, the caller's tag, the checksum of the rows file it belongs
+// to, the number of paths, a hash of everything behind the header), then per path a length and the bytes.
+// A path table left over from another save of the same size, or one whose rows file was replaced, is
+// refused: both files must come from the same lkx_save.
+struct PathsHeader {
+    char magic[8];  // "LKPTH001"
+    uint64_t tag, rows_checksum, n, body_hash;
+};
+static_assert(sizeof(PathsHeader) == 40, "paths header layout");
+
 int lkx_save(lkx_index *x, const char *path, uint64_t tag) {
     if (!x || !path) return fail(LK_EINVAL, "lkx_save: bad argument");
     if (!x->dev) return fail(LK_EINVAL, "lkx_save: the index is empty");
     LK_TRY(lk_index_save(x->dev, path, tag));
+    PathsHeader h;
+    memcpy(h.magic, "LKPTH001", 8);
+    uint64_t rows_tag = 0;
+    LK_TRY(cache_identity(path, &rows_tag, &h.rows_checksum));
+    h.tag = tag;
+    h.n = x->paths.size();
+    std::string body;
+    for (const std::string &p : x->paths) {
+        const uint32_t len = (uint32_t)p.size();
+        body.append((const char *)&len, 4);
+        body.append(p);
+    }
+    h.body_hash = cache_hash(body.data(), body.size(), h.rows_checksum);
     const std::string names = std::string(path) + ".paths", tmp = names + ".tmp";
     FILE *f = fopen(tmp.c_str(), "wb");
     if (!f) return fail(LK_EINVAL, "lkx_save: cannot create " + tmp);
-    bool ok = true;
-    const uint64_t n = x->paths.size();
-    ok = ok && fwrite(&n, 8, 1, f) == 1;
-    for (const std::string &p : x->paths) {
-        const uint32_t len = (uint32_t)p.size();
-        ok = ok && fwrite(&len, 4, 1, f) == 1 && (len == 0 || fwrite(p.data(), 1, len, f) == len);
-    }
+    bool ok = fwrite(&h, sizeof(h), 1, f) == 1 && (body.empty() || fwrite(body.data(), 1, body.size(), f) == body.size());
     ok = (fclose(f) == 0) && ok;
     if (!ok || rename(tmp.c_str(), names.c_str()) != 0) {
         remove(tmp.c_str());
@@ -291,6 +315,23 @@ int lkx_save(lkx_index *x, const char *path, uint64_t tag) {
 int lkx_load(const char *path, uint64_t tag, int device, lkx_index **out) {
     if (!path || !out) return fail(LK_EINVAL, "lkx_load: bad argument");
     *out = nullptr;
+    // the path table first: it is small, and a mismatch spares the upload of the rows
+    const std::string names = std::string(path) + ".paths";
+    uint64_t rows_tag = 0, rows_checksum = 0;
+    LK_TRY(cache_identity(path, &rows_tag, &rows_checksum));
+    FILE *f = fopen(names.c_str(), "rb");
+    PathsHeader h;
+    bool ok = f != nullptr && fread(&h, sizeof(h), 1, f) == 1 && memcmp(h.magic, "LKPTH001", 8) == 0 && h.tag == tag &&
+              rows_tag == tag && h.rows_checksum == rows_checksum && h.n <= 0xfffffff0ull;
+    std::string body;
+    if (ok) {
+        char buf[1 << 16];
+        size_t got;
+        while ((got = fread(buf, 1, sizeof(buf), f)) > 0) body.append(buf, got);
+        ok = cache_hash(body.data(), body.size(), h.rows_checksum) == h.body_hash;
+    }
+    if (f) fclose(f);
+    if (!ok) return fail(LK_EINVAL, "lkx_load: " + names + " is missing, damaged, or does not belong to these cached rows");
     lk_index *dev = nullptr;
     LK_TRY(lk_index_load(path, tag, device, &dev));
     lkx_index *x = new (std::nothrow) lkx_index();
@@ -302,25 +343,25 @@ int lkx_load(const char *path, uint64_t tag, int device, lkx_index **out) {
     x->dim = lk_index_dim(dev);
     x->device = device;
     lk_index_kind(dev, &x->store, &x->centered);
-    const std::string names = std::string(path) + ".paths";
-    FILE *f = fopen(names.c_str(), "rb");
-    bool ok = f != nullptr;
-    uint64_t n = 0;
-    ok = ok && fread(&n, 8, 1, f) == 1 && (int64_t)n == lk_index_len(dev);
-    for (uint64_t i = 0; ok && i < n; ++i) {
+    ok = (int64_t)h.n == lk_index_len(dev);
+    size_t at = 0;
+    for (uint64_t i = 0; ok && i < h.n; ++i) {
         uint32_t len = 0;
-        ok = fread(&len, 4, 1, f) == 1 && len < (1u << 20);
-        std::string p(len, '\0');
-        ok = ok && (len == 0 || fread(&p[0], 1, len, f) == len);
+        ok = at + 4 <= body.size();
+        if (ok) memcpy(&len, body.data() + at, 4);
+        at += 4;
+        ok = ok && len < (1u << 20) && at + len <= body.size();
         if (ok) {
+            std::string p(body.data() + at, len);
+            at += len;
             ok = x->slot.emplace(p, (int64_t)i).second;  // a path can own one slot only
             x->paths.emplace_back(std::move(p));
         }
     }
-    if (f) fclose(f);
+    ok = ok && at == body.size();
     if (!ok) {
         lkx_free(x);
-        return fail(LK_EINVAL, "lkx_load: " + names + " is missing or does not match the cached rows");
+        return fail(LK_EINVAL, "lkx_load: " + names + " does not match the cached rows");
     }
     *out = x;
     return LK_OK;

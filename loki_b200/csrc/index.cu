@@ -1119,7 +1119,7 @@ int lk_stats(lk_index *idx, lk_stats_t *out) {
 namespace {
 
 struct CacheHeader {  // 128 bytes, little-endian like the machine
-    char magic[8];    // "LKIDX001"
+    char magic[8];    // "LKIDX002"
     int32_t dim, store, centered, center_live;
     int64_t len, ld, n_centered;
     uint64_t tag, checksum;
@@ -1216,6 +1216,29 @@ int fill_device(lk_index *idx, void *d, size_t bytes, FILE *f, CachePipe &pp, Ha
 
 }  // namespace
 
+namespace lk {
+
+// For the path table kept beside a cache file (host_index.cu): the tag and checksum in the header
+// of the rows file, and the hash used for both files.
+int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum) {
+    FILE *f = fopen(path, "rb");
+    CacheHeader h;
+    const bool ok = f != nullptr && fread(&h, 1, sizeof(h), f) == sizeof(h) && memcmp(h.magic, "LKIDX002", 8) == 0;
+    if (f) fclose(f);
+    if (!ok) return fail(LK_EINVAL, std::string("cannot read the cache header of ") + path);
+    *tag = h.tag;
+    *checksum = h.checksum;
+    return 0;
+}
+uint64_t cache_hash(const void *p, size_t n, uint64_t seed) {
+    Hasher hs;
+    hs.add(&seed, sizeof(seed));
+    hs.add(p, n);
+    return hs.value();
+}
+
+}  // namespace lk
+
 extern "C" {
 
 int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
@@ -1230,7 +1253,7 @@ int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
     int st = pin.init();
     CacheHeader h;
     memset(&h, 0, sizeof(h));
-    memcpy(h.magic, "LKIDX001", 8);
+    memcpy(h.magic, "LKIDX002", 8);
     h.dim = idx->dim;
     h.store = idx->store;
     h.centered = idx->centered;
@@ -1254,6 +1277,7 @@ int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
         }
     }
     if (st == 0) {
+        hs.add(&h, sizeof(h));  // the header's own fields (checksum still zero) are covered too
         h.checksum = hs.value();
         if (fseek(f, 0, SEEK_SET) != 0 || fwrite(&h, 1, sizeof(h), f) != sizeof(h)) st = fail(LK_EINVAL, "lk_index_save: write failed");
     }
@@ -1270,7 +1294,7 @@ int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out) {
     if (!f) return fail(LK_EINVAL, std::string("lk_index_load: cannot open ") + path);
     CacheHeader h;
     int st = 0;
-    if (fread(&h, 1, sizeof(h), f) != sizeof(h) || memcmp(h.magic, "LKIDX001", 8) != 0)
+    if (fread(&h, 1, sizeof(h), f) != sizeof(h) || memcmp(h.magic, "LKIDX002", 8) != 0)
         st = fail(LK_EINVAL, "lk_index_load: not an index cache of this version");
     else if (h.tag != tag)
         st = fail(LK_EINVAL, "lk_index_load: the cache was written for another tag (model or row count changed)");
@@ -1303,6 +1327,11 @@ int lk_index_load(const char *path, uint64_t tag, int device, lk_index **out) {
         }
     }
     if (st == 0 && fgetc(f) != EOF) st = fail(LK_EINVAL, "lk_index_load: the file is longer than its header says");
+    if (st == 0) {
+        CacheHeader plain = h;
+        plain.checksum = 0;
+        hs.add(&plain, sizeof(plain));
+    }
     if (st == 0 && hs.value() != h.checksum) st = fail(LK_EINVAL, "lk_index_load: checksum mismatch, the cache is damaged");
     fclose(f);
     if (st != 0) {

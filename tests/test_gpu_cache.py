@@ -87,3 +87,36 @@ def test_path_keyed_cache(lk, tmp_path):
     os.remove(path + ".paths")
     with pytest.raises(E.LokiError, match="paths"):
         E.VectorIndex.LoadCache(path, tag=len(names))
+
+
+def test_path_table_must_belong_to_its_rows(lk, tmp_path):
+    """A path table left over from another save (same row count, same tag) or with a flipped byte is
+    refused: both files must come from the same save, and the header's own fields are checksummed."""
+    from loki_b200 import embedindex as E
+    names = [f"/lib/{i:04d}.jpg" for i in range(300)]
+    rows = _rows(300, 32, 9)
+    a = E.New()
+    a.AddBatch(names, rows)
+    b = E.New()
+    b.AddBatch(list(reversed(names)), rows)                 # same count, other path order
+    pa, pb = str(tmp_path / "a.lkidx"), str(tmp_path / "b.lkidx")
+    a.SaveCache(pa, tag=300)
+    b.SaveCache(pb, tag=300)
+    assert E.VectorIndex.LoadCache(pa, tag=300).Len() == 300
+    stale = open(pb + ".paths", "rb").read()
+    good = open(pa + ".paths", "rb").read()
+    open(pa + ".paths", "wb").write(stale)                  # the other save's table beside these rows
+    with pytest.raises(E.LokiError, match="paths"):
+        E.VectorIndex.LoadCache(pa, tag=300)
+    flipped = bytearray(good)
+    flipped[-3] ^= 0x01                                     # one bit inside a path
+    open(pa + ".paths", "wb").write(bytes(flipped))
+    with pytest.raises(E.LokiError, match="paths"):
+        E.VectorIndex.LoadCache(pa, tag=300)
+    open(pa + ".paths", "wb").write(good)
+    assert [h.Path for h in E.VectorIndex.LoadCache(pa, tag=300).Search(rows[5], 3)] == [h.Path for h in a.Search(rows[5], 3)]
+    blob = bytearray(open(pa, "rb").read())
+    blob[40] ^= 0x01                                        # a header field of the rows file (n_centered's neighbourhood)
+    open(pa, "wb").write(bytes(blob))
+    with pytest.raises(E.LokiError):
+        E.VectorIndex.LoadCache(pa, tag=300)
