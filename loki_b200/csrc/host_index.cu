@@ -14,7 +14,7 @@
 #include "lk_common.cuh"
 
 namespace lk {  // index.cu
-int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum);
+int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum, uint64_t *save_id);
 uint64_t cache_hash(const void *p, size_t n, uint64_t seed);
 }  // namespace lk
 
@@ -273,15 +273,16 @@ void lkx_hits_free(lkx_hits *h) { delete h; }
 
 // ---- on-disk cache: the device-side file of lk_index_save plus the paths in slot order ----
 
-// `<path>.paths`: a 40-byte header (magic, the caller's tag, the checksum of the rows file it belongs
-// to, the number of paths, a hash of everything behind the header), then per path a length and the bytes.
+// `<path>.paths`: a 48-byte header (magic, the caller's tag, the checksum and the save number of the rows
+// file it belongs to, the number of paths, a hash of everything behind the header), then per path a
+// length and the bytes.
 // A path table left over from another save of the same size, or one whose rows file was replaced, is
 // refused: both files must come from the same lkx_save.
 struct PathsHeader {
     char magic[8];  // "LKPTH001"
-    uint64_t tag, rows_checksum, n, body_hash;
+    uint64_t tag, rows_checksum, rows_save_id, n, body_hash;
 };
-static_assert(sizeof(PathsHeader) == 40, "paths header layout");
+static_assert(sizeof(PathsHeader) == 48, "paths header layout");
 
 int lkx_save(lkx_index *x, const char *path, uint64_t tag) {
     if (!x || !path) return fail(LK_EINVAL, "lkx_save: bad argument");
@@ -290,7 +291,7 @@ int lkx_save(lkx_index *x, const char *path, uint64_t tag) {
     PathsHeader h;
     memcpy(h.magic, "LKPTH001", 8);
     uint64_t rows_tag = 0;
-    LK_TRY(cache_identity(path, &rows_tag, &h.rows_checksum));
+    LK_TRY(cache_identity(path, &rows_tag, &h.rows_checksum, &h.rows_save_id));
     h.tag = tag;
     h.n = x->paths.size();
     std::string body;
@@ -317,12 +318,12 @@ int lkx_load(const char *path, uint64_t tag, int device, lkx_index **out) {
     *out = nullptr;
     // the path table first: it is small, and a mismatch spares the upload of the rows
     const std::string names = std::string(path) + ".paths";
-    uint64_t rows_tag = 0, rows_checksum = 0;
-    LK_TRY(cache_identity(path, &rows_tag, &rows_checksum));
+    uint64_t rows_tag = 0, rows_checksum = 0, rows_save_id = 0;
+    LK_TRY(cache_identity(path, &rows_tag, &rows_checksum, &rows_save_id));
     FILE *f = fopen(names.c_str(), "rb");
     PathsHeader h;
     bool ok = f != nullptr && fread(&h, sizeof(h), 1, f) == 1 && memcmp(h.magic, "LKPTH001", 8) == 0 && h.tag == tag &&
-              rows_tag == tag && h.rows_checksum == rows_checksum && h.n <= 0xfffffff0ull;
+              rows_tag == tag && h.rows_checksum == rows_checksum && h.rows_save_id == rows_save_id && h.n <= 0xfffffff0ull;
     std::string body;
     if (ok) {
         char buf[1 << 16];

@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <unistd.h>
 #include <mutex>
 #include <new>
 #include <string>
@@ -1124,7 +1125,8 @@ struct CacheHeader {  // 128 bytes, little-endian like the machine
     int64_t len, ld, n_centered;
     uint64_t tag, checksum;
     double mu_n2;
-    unsigned char pad[56];
+    uint64_t save_id;  // a number drawn at every save: what ties a path table to exactly this file
+    unsigned char pad[48];
 };
 static_assert(sizeof(CacheHeader) == 128, "cache header layout");
 
@@ -1220,7 +1222,7 @@ namespace lk {
 
 // For the path table kept beside a cache file (host_index.cu): the tag and checksum in the header
 // of the rows file, and the hash used for both files.
-int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum) {
+int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum, uint64_t *save_id) {
     FILE *f = fopen(path, "rb");
     CacheHeader h;
     const bool ok = f != nullptr && fread(&h, 1, sizeof(h), f) == sizeof(h) && memcmp(h.magic, "LKIDX002", 8) == 0;
@@ -1228,6 +1230,7 @@ int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum) {
     if (!ok) return fail(LK_EINVAL, std::string("cannot read the cache header of ") + path);
     *tag = h.tag;
     *checksum = h.checksum;
+    *save_id = h.save_id;
     return 0;
 }
 uint64_t cache_hash(const void *p, size_t n, uint64_t seed) {
@@ -1263,6 +1266,8 @@ int lk_index_save(lk_index *idx, const char *path, uint64_t tag) {
     h.n_centered = idx->n_centered;
     h.tag = tag;
     h.mu_n2 = idx->mu_n2;
+    h.save_id = (uint64_t)std::chrono::steady_clock::now().time_since_epoch().count() * 0x9e3779b97f4a7c15ull ^
+                (uint64_t)(uintptr_t)idx ^ ((uint64_t)getpid() << 32);
     Hasher hs;
     if (st == 0 && fwrite(&h, 1, sizeof(h), f) != sizeof(h)) st = fail(LK_EINVAL, "lk_index_save: write failed");
     if (st == 0 && idx->len > 0) st = dump_device(idx, idx->d_rows, (size_t)idx->len * idx->ld, f, pin, hs);

@@ -98,7 +98,7 @@ struct ResultArena {
 };
 
 // identity of a cache file written by lk_index_save, and the hash both cache files use (index.cu)
-int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum);
+int cache_identity(const char *path, uint64_t *tag, uint64_t *checksum, uint64_t *save_id);
 uint64_t cache_hash(const void *p, size_t n, uint64_t seed);
 
 }  // namespace lk
