@@ -228,7 +228,7 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
 // caller repeats the scan without the bound, so the result is exact either way.
 // ---------------------------------------------------------------------------
 constexpr int kFloorMinK = 256;       // below this the per-CTA lists are cheap anyway
-constexpr int kSampleMin = 8192, kSampleMax = 65536;
+constexpr int kSampleMin = 8192, kSampleMax = 32768;
 
 __global__ void k_fill_stride(int *slots, int n, long long len) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
@@ -244,7 +244,7 @@ static bool floor_applies(const lk_index *idx, bool filtered, bool sharded, int 
 // receives the device address of the bound.
 static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const unsigned char *inl, bool centered, float cq,
                                float qscale, int k_eff, const unsigned long long **floor_out) {
-    const int S = (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 32)) & ~31;
+    const int S = (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 64)) & ~31;
     const double r = (double)k_eff * S / (double)idx->len;
     const double x = (5.0 + std::sqrt(25.0 + 4.0 * r)) * 0.5;  // r' - 5 sqrt(r') >= r
     const int rr = std::min<int>(kMaxK, std::max<int>(16, (int)std::ceil(x * x)));

@@ -234,7 +234,7 @@ def test_large_k_scan_when_the_sample_misleads(lk):
     n, dim, k = 524_288, 64, 400
     rows = gaussian_rows(n, dim, 5150)
     q = gaussian_rows(1, dim, 5151)[0]
-    stride = 32                                   # the sample takes every 32nd row of an index of this size
+    stride = 64                                   # the sample takes every 64th row of an index of this size
     rng = np.random.default_rng(5)
     rows[::stride] = q + 0.05 * rng.standard_normal((n // stride, dim)).astype(np.float32)
     for store in (lk.LK_I8, lk.LK_F32):
