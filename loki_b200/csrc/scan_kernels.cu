@@ -340,18 +340,33 @@ __device__ __forceinline__ int peer_merge_emit(const PeerTable &pt, unsigned seq
 
 // Shared tail of both scan kernels: publish this CTA's list; the last CTA to arrive
 // merges all lists and writes the result.
+// `spare` / `spare_keys`: shared memory the CTA no longer needs once it is out of rows (the
+// streaming kernels' stage buffers).  The last CTA merges there when k is large: the keys above the
+// merge's starting threshold number between k and a few k, and the CTA's own buffer (sized for k plus
+// one round of appends) would often overflow, which costs a second, slower pass.
 template <int TYPE>
-__device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const CandBuf &buf, int *s_last) {
+__device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const CandBuf &own, int *s_last,
+                                                   unsigned long long *spare = nullptr, int spare_keys = 0) {
     const int tid = threadIdx.x, T = blockDim.x;
     unsigned long long *mine = a.part + (size_t)blockIdx.x * a.k;
-    for (int i = tid; i < a.k; i += T) mine[i] = buf.keys[i];
-    if (tid == 0 && a.part_cnt != nullptr) a.part_cnt[blockIdx.x] = min(buf.ctrl->count, a.k);
+    for (int i = tid; i < a.k; i += T) mine[i] = own.keys[i];
+    if (tid == 0 && a.part_cnt != nullptr) a.part_cnt[blockIdx.x] = min(own.ctrl->count, a.k);
     __threadfence();
     __syncthreads();
     if (tid == 0) *s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
     __syncthreads();
     if (!*s_last) return;
     __threadfence();
+    CandBuf buf = own;
+    if (a.k > 32 && spare != nullptr) {
+        int want = own.cap;
+        while (want < 4 * a.k && want * 2 <= spare_keys) want <<= 1;
+        if (want > own.cap) {
+            buf.keys = spare;
+            buf.cap = want;
+            buf.limit = want - kScanThreads;
+        }
+    }
     if (a.k <= 32 && (int)(blockDim.x >> 5) * 32 <= buf.cap)
         cand_select_small(buf, a.part, (int)gridDim.x);
     else if (!cand_select_flat(buf, a.part, a.part_cnt, (int)gridDim.x))
@@ -755,7 +770,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
     // with the previous launch on the stream (per-CTA lists, ticket) is next: wait until
     // that launch has completely finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    publish_and_finish<TYPE>(a, buf, &s_last);
+    __syncthreads();  // every warp is done with its stages: they are the last CTA's merge space
+    publish_and_finish<TYPE>(a, buf, &s_last, reinterpret_cast<unsigned long long *>(stages),
+                             (int)((size_t)WARPS * kBulkStages * stage_bytes / 8));
 }
 
 // ---------------------------------------------------------------------------
@@ -949,7 +966,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
         }
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    publish_and_finish<TYPE>(a, buf, &s_last);
+    __syncthreads();  // every warp is done with its stages: they are the last CTA's merge space
+    publish_and_finish<TYPE>(a, buf, &s_last, reinterpret_cast<unsigned long long *>(stages),
+                             (int)((size_t)WARPS * kBulkStages * STAGE / 8));
 }
 
 // ---------------------------------------------------------------------------
@@ -1354,8 +1373,10 @@ int scan_launch(int type, const ScanArgs &a, const ScanPlan &plan, cudaStream_t 
         if (le != cudaSuccess) return fail(4, std::string("scan launch: ") + cudaGetErrorString(le));
     } else {
         scan_fn fn = pick(type, plan.g);
+        // never more CTAs than give every warp of a CTA a batch: fewer lists for the last CTA to merge
         int grid = plan.grid;
-        if (batches < grid) grid = (int)(batches > 0 ? batches : 1);  // never more CTAs than batches
+        const long long full = batches / kScanWarps;
+        if (full < grid) grid = (int)(full > 0 ? full : 1);
         fn<<<grid, kScanThreads, plan.smem, stream>>>(a);
     }
     cudaError_t e = cudaGetLastError();
