@@ -43,6 +43,107 @@ struct CandBuf {
     int k;
 };
 
+// ---------------------------------------------------------------------------
+// Bitonic sort (descending) of sz keys in shared memory by the whole CTA; sz is a power of two,
+// at least kSortSegment.  The network's compare-exchanges between keys fewer than kSortSegment
+// apart stay inside an aligned segment of 256 keys, and a warp does them with the segment in
+// registers: lane l holds keys 8l..8l+7, partners 1, 2 or 4 apart meet in the lane's own registers
+// and partners 8..128 apart through warp shuffles.  All phases up to 256 keys therefore need no
+// barrier at all, and each later phase needs one barrier per stride of 256 and up plus one for
+// its register part: 14 barriers for 2,048 keys, where a sort through shared memory takes 66.
+// Not inlined: the network is a few thousand instructions, and the scan kernels exist in dozens of
+// instantiations.  Every thread of the CTA calls it; the keys are visible to all threads on return.
+// ---------------------------------------------------------------------------
+constexpr int kSortSegment = 256;
+
+__device__ __forceinline__ void sort_cx(unsigned long long &lo, unsigned long long &hi, bool desc) {
+    const bool sw = (lo < hi) == desc;  // descending: the larger key belongs at the lower index
+    const unsigned long long t = lo;
+    lo = sw ? hi : lo;
+    hi = sw ? t : hi;
+}
+
+// strides 4, 2, 1 (those not above FIRST) of phase `size` on a lane's eight keys; i0 = index of v[0]
+template <int FIRST>
+__device__ __forceinline__ void sort_reg_steps(unsigned long long (&v)[8], int i0, int size) {
+#pragma unroll
+    for (int stride = 4; stride > 0; stride >>= 1) {
+        if (stride > FIRST) continue;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if ((e & stride) == 0) sort_cx(v[e], v[e + stride], ((i0 + e) & size) == 0);
+    }
+}
+
+// strides 8*first, ..., 16, 8 of phase `size` (at least 16): partners sit in lanes first, ..., 2, 1 apart
+__device__ __forceinline__ void sort_lane_steps(unsigned long long (&v)[8], int i0, int size, int first, int lane) {
+    const bool desc = (i0 & size) == 0;  // the same for a lane's eight keys and for its partner's
+    for (int ls = first; ls > 0; ls >>= 1) {
+        const bool keep_larger = ((lane & ls) == 0) == desc;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const unsigned long long o = shfl_xor_u64(v[e], ls);
+            v[e] = ((v[e] > o) == keep_larger) ? v[e] : o;
+        }
+    }
+}
+
+__device__ __noinline__ inline void block_sort_desc(unsigned long long *keys, int sz) {
+    const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, warps = T >> 5;
+    const unsigned base = (unsigned)__cvta_generic_to_shared(keys);
+    auto load8 = [&](int i0, unsigned long long (&v)[8]) {
+#pragma unroll
+        for (int e = 0; e < 8; e += 2)
+            asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v[e]), "=l"(v[e + 1]) : "r"(base + (unsigned)(i0 + e) * 8u));
+    };
+    auto store8 = [&](int i0, const unsigned long long (&v)[8]) {
+#pragma unroll
+        for (int e = 0; e < 8; e += 2)
+            asm volatile("st.shared.v2.u64 [%2], {%0, %1};" ::"l"(v[e]), "l"(v[e + 1]), "r"(base + (unsigned)(i0 + e) * 8u) : "memory");
+    };
+    // phases 2 .. 256: whole segments, no barrier
+    for (int seg = warp * kSortSegment; seg < sz; seg += warps * kSortSegment) {
+        const int i0 = seg + lane * 8;
+        unsigned long long v[8];
+        load8(i0, v);
+        sort_reg_steps<1>(v, i0, 2);
+        sort_reg_steps<2>(v, i0, 4);
+        sort_reg_steps<4>(v, i0, 8);
+#pragma unroll 1
+        for (int size = 16; size <= kSortSegment; size <<= 1) {
+            sort_lane_steps(v, i0, size, size >> 4, lane);
+            sort_reg_steps<4>(v, i0, size);
+        }
+        store8(i0, v);
+    }
+    __syncthreads();
+    for (int size = 2 * kSortSegment; size <= sz; size <<= 1) {
+        for (int stride = size >> 1; stride >= kSortSegment; stride >>= 1) {
+            for (int i = tid; i < (sz >> 1); i += T) {
+                const int pos = 2 * i - (i & (stride - 1));
+                const unsigned pa = base + (unsigned)pos * 8u, pb = pa + (unsigned)stride * 8u;
+                unsigned long long x, y;
+                asm volatile("ld.shared.u64 %0, [%1];" : "=l"(x) : "r"(pa));
+                asm volatile("ld.shared.u64 %0, [%1];" : "=l"(y) : "r"(pb));
+                if ((x < y) == ((pos & size) == 0)) {
+                    asm volatile("st.shared.u64 [%0], %1;" ::"r"(pa), "l"(y) : "memory");
+                    asm volatile("st.shared.u64 [%0], %1;" ::"r"(pb), "l"(x) : "memory");
+                }
+            }
+            __syncthreads();
+        }
+        for (int seg = warp * kSortSegment; seg < sz; seg += warps * kSortSegment) {
+            const int i0 = seg + lane * 8;
+            unsigned long long v[8];
+            load8(i0, v);
+            sort_lane_steps(v, i0, size, 16, lane);
+            sort_reg_steps<4>(v, i0, size);
+            store8(i0, v);
+        }
+        __syncthreads();
+    }
+}
+
 // Sort keys[0..count) descending, keep the best k, zero the rest, raise thr.
 // Must be called by all threads of the CTA with `count` stable.
 __device__ inline void cand_prune(const CandBuf &b) {
@@ -74,74 +175,11 @@ __device__ inline void cand_prune(const CandBuf &b) {
         __syncthreads();
         return;
     }
-    int sz = 2;
+    int sz = kSortSegment;  // (every buffer holds at least 512 keys)
     while (sz < c) sz <<= 1;
     for (int i = c + tid; i < sz; i += T) b.keys[i] = 0ull;
     __syncthreads();
-    // Bitonic sort, descending.  Compare-exchanges whose partners lie fewer than kSortRun keys apart
-    // stay inside an aligned run of kSortRun keys: a thread takes such a run into registers and does
-    // all those steps of a phase without a barrier; only the wider strides go through shared memory
-    // with a barrier per step (28 instead of 66 for 2,048 keys).
-    constexpr int kSortRun = 16;
-    auto run_steps = [&](int size, int first_stride) {  // strides first_stride, first_stride/2, ..., 1 of phase `size`
-        for (int r0 = tid * kSortRun; r0 < sz; r0 += T * kSortRun) {
-            unsigned long long v[kSortRun];
-#pragma unroll
-            for (int e = 0; e < kSortRun; ++e) v[e] = b.keys[r0 + e];
-#pragma unroll
-            for (int stride = kSortRun / 2; stride > 0; stride >>= 1) {
-                if (stride <= first_stride) {
-#pragma unroll
-                    for (int e = 0; e < kSortRun; ++e) {
-                        if ((e & stride) == 0) {
-                            const bool desc = ((r0 + e) & size) == 0;
-                            const unsigned long long x = v[e], y = v[e + stride];
-                            if ((x < y) == desc) {
-                                v[e] = y;
-                                v[e + stride] = x;
-                            }
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < kSortRun; ++e) b.keys[r0 + e] = v[e];
-        }
-        __syncthreads();
-    };
-    if (sz < kSortRun) {  // (c > 32 here, so this does not happen; kept for completeness of the routine)
-        for (int size = 2; size <= sz; size <<= 1) {
-            for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                for (int i = tid; i < (sz >> 1); i += T) {
-                    int pos = 2 * i - (i & (stride - 1));
-                    unsigned long long x = b.keys[pos], y = b.keys[pos + stride];
-                    bool desc = (pos & size) == 0;
-                    if ((x < y) == desc) {
-                        b.keys[pos] = y;
-                        b.keys[pos + stride] = x;
-                    }
-                }
-                __syncthreads();
-            }
-        }
-    } else {
-        for (int size = 2; size <= sz; size <<= 1) {
-            int stride = size >> 1;
-            for (; stride >= kSortRun; stride >>= 1) {
-                for (int i = tid; i < (sz >> 1); i += T) {
-                    int pos = 2 * i - (i & (stride - 1));
-                    unsigned long long x = b.keys[pos], y = b.keys[pos + stride];
-                    bool desc = (pos & size) == 0;
-                    if ((x < y) == desc) {
-                        b.keys[pos] = y;
-                        b.keys[pos + stride] = x;
-                    }
-                }
-                __syncthreads();
-            }
-            run_steps(size, stride);
-        }
-    }
+    block_sort_desc(b.keys, sz);
     const int keep = c < b.k ? c : b.k;
     for (int i = keep + tid; i < sz; i += T) b.keys[i] = 0ull;
     if (tid == 0) {
