@@ -195,6 +195,7 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
     a.k = k;
     a.bound = nullptr;
     a.floor = nullptr;
+    a.floor_wait = 0;
     a.part = (unsigned long long *)idx->part.p;
     a.part_cnt = idx->part.p ? (int *)((unsigned char *)idx->part.p + idx->part.bytes - kPartCntBytes) : nullptr;
     a.ticket = idx->d_ticket;
@@ -229,6 +230,7 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
 // ---------------------------------------------------------------------------
 constexpr int kFloorMinK = 256;       // below this the per-CTA lists are cheap anyway
 constexpr int kSampleMin = 8192, kSampleMax = 32768;
+constexpr int kFloorChunk = 64;       // queries of a batch whose sample scans are issued together, ahead of their scans
 
 __global__ void k_fill_stride(int *slots, int n, long long len) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
@@ -241,9 +243,11 @@ static bool floor_applies(const lk_index *idx, bool filtered, bool sharded, int 
 }
 
 // Enqueue the sample scan of one prepared query (in device memory, or inline in `inl`); *floor_out
-// receives the device address of the bound.
+// receives the device address of the bound.  A batch issues the sample scans of up to kFloorChunk
+// queries first (`blocks` of them, this one writing output block `block`) and the real scans after
+// them: the real scans then follow one another directly and overlap at their edges.
 static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const unsigned char *inl, bool centered, float cq,
-                               float qscale, int k_eff, const unsigned long long **floor_out) {
+                               float qscale, int k_eff, const unsigned long long **floor_out, int block = 0, int blocks = 1) {
     const int S = (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 64)) & ~31;
     const double r = (double)k_eff * S / (double)idx->len;
     const double x = (5.0 + std::sqrt(25.0 + 4.0 * r)) * 0.5;  // r' - 5 sqrt(r') >= r
@@ -252,11 +256,12 @@ static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const un
         LK_TRY(scan_plan(idx->type, idx->chunks, rr, idx->device, &idx->plan_sample));
         idx->plan_sample_k = rr;
     }
-    // slots [S] | keys [rr] | ids [rr] | scores [rr] | iscores [rr] | count
-    const size_t o_keys = (size_t)round_up((int64_t)S * 4, 256), o_ids = o_keys + (size_t)rr * 8, o_sc = o_ids + (size_t)rr * 8;
-    const size_t o_isc = o_sc + (size_t)rr * 4, o_cnt = o_isc + (size_t)rr * 4;
+    // slots [S] | per block: keys [rr] | ids [rr] | scores [rr] | iscores [rr] | count
+    const size_t block_bytes = (size_t)round_up((int64_t)rr * 24 + 16, 256);
+    const size_t o_keys = (size_t)round_up((int64_t)S * 4, 256) + (size_t)block * block_bytes, o_ids = o_keys + (size_t)rr * 8;
+    const size_t o_sc = o_ids + (size_t)rr * 8, o_isc = o_sc + (size_t)rr * 4, o_cnt = o_isc + (size_t)rr * 4;
     const void *before = idx->d_sample.p;
-    LK_TRY(idx->d_sample.reserve(o_cnt + 16));
+    LK_TRY(idx->d_sample.reserve((size_t)round_up((int64_t)S * 4, 256) + (size_t)std::max(blocks, block + 1) * block_bytes));
     if (idx->d_sample.p != before || idx->sample_len != idx->len || idx->sample_n != S) {
         k_fill_stride<<<64, 256, 0, idx->stream>>>((int *)idx->d_sample.p, S, idx->len);
         LK_CUDA(cudaGetLastError());
@@ -285,14 +290,13 @@ static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const un
 static int enqueue_query(lk_index *idx, const unsigned char *d_q, bool centered, float cq, float qscale,
                          const int *d_slots, long long n_cand, int k_eff, int k_stride, int passes,
                          const ResultArena &res, int qi, const PeerTable *peer = nullptr, unsigned int seq = 0,
-                         int batch_pos = 0, bool use_floor = false) {
-    const unsigned long long *floor = nullptr;
-    if (use_floor) LK_TRY(enqueue_sample_scan(idx, d_q, nullptr, centered, cq, qscale, k_eff, &floor));
+                         int batch_pos = 0, const unsigned long long *floor = nullptr, bool floor_wait = false) {
     for (int p = 0; p < passes; ++p) {
         const int done = p * kMaxK;
         ScanArgs a = base_args(idx, centered, cq, qscale, d_slots, n_cand, std::min(kMaxK, k_eff - done));
         a.query = d_q;
         a.floor = floor;
+        a.floor_wait = floor_wait ? 1 : 0;
         const size_t o = (size_t)qi * k_stride + done;
         a.bound = (p == 0) ? nullptr : res.d_keys() + o - 1;
         a.out_keys = res.d_keys() + o;
@@ -500,6 +504,7 @@ static int search_one_fast(lk_index *idx, const float *query, int scoring, const
     const bool use_floor = floor_applies(idx, d_slots != nullptr, peer != nullptr || idx->comm != nullptr, k_eff, 1);
     if (use_floor) {
         LK_TRY(enqueue_sample_scan(idx, nullptr, a.query_inline, centered, cq, qscale, k_eff, &a.floor));
+        a.floor_wait = 1;
         a.part = (unsigned long long *)idx->part.p;  // the sample scan may have grown the scratch
         a.part_cnt = (int *)((unsigned char *)idx->part.p + idx->part.bytes - kPartCntBytes);
     }
@@ -842,10 +847,18 @@ int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring, c
     // sharded: exchange inside the scan kernel over peer memory when that is set up, else NCCL
     unsigned int seq = 0;
     const bool use_floor = floor_applies(idx, filtered, sharded, k_eff, passes);
+    const unsigned long long *floors[kFloorChunk] = {};
     for (int q = 0; q < nq; ++q) {
+        const int c = q % kFloorChunk, chunk = std::min(kFloorChunk, nq - (q - c));
+        if (use_floor && c == 0)  // the sample scans of the next chunk of queries, then their scans
+            for (int j = 0; j < chunk; ++j)
+                LK_TRY(enqueue_sample_scan(idx, (const unsigned char *)idx->d_query.p + (size_t)(q + j) * idx->qbytes, nullptr,
+                                           cen[q + j] != 0, cq[q + j], qscale[q + j], k_eff, &floors[j], j, chunk));
         seq = peer ? comm_next_seq(idx->comm) : 0u;
+        // only the chunk's last sample scan can still be running when a scan of the chunk starts
         LK_TRY(enqueue_query(idx, (const unsigned char *)idx->d_query.p + (size_t)q * idx->qbytes, cen[q] != 0, cq[q],
-                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer, seq, q, use_floor));
+                             qscale[q], d_slots, n_cand, k_eff, k_eff, passes, idx->res, q, peer, seq, q,
+                             use_floor ? floors[c] : nullptr, c == chunk - 1));
     }
     if (peer) LK_TRY(drain_queued(idx, peer, idx->res, nq - 1, seq, nq, k_eff));
     if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, idx->res, 0, nq, k_eff));
@@ -1020,10 +1033,21 @@ int lk_search_resident(lk_index *idx, lk_queries *q, int first, int count, int k
     if (q->res.nq != q->nq || q->res.k != k_eff) LK_TRY(q->res.shape(q->nq, k_eff, 1));
     const PeerTable *peer = sharded ? comm_peer_table(idx->comm, k_eff) : nullptr;
     unsigned int seq = 0;
+    // large k: sampled floors, the queries that come out short are repeated without one by lk_queries_fetch
+    const bool use_floor = floor_applies(idx, false, sharded, k_eff, 1);
+    const unsigned long long *floors[kFloorChunk] = {};
+    q->floored.resize((size_t)q->nq, 0);
     for (int i = first; i < first + count; ++i) {
+        const int c = (i - first) % kFloorChunk, chunk = std::min(kFloorChunk, first + count - (i - c));
+        if (use_floor && c == 0)
+            for (int j = 0; j < chunk; ++j)
+                LK_TRY(enqueue_sample_scan(idx, (const unsigned char *)q->d_query.p + (size_t)(i + j) * idx->qbytes, nullptr,
+                                           q->centered != 0, q->cq[i + j], q->qscale[i + j], k_eff, &floors[j], j, chunk));
+        q->floored[(size_t)i] = use_floor ? 1 : 0;
         seq = peer ? comm_next_seq(idx->comm) : 0u;
         LK_TRY(enqueue_query(idx, (const unsigned char *)q->d_query.p + (size_t)i * idx->qbytes, q->centered != 0,
-                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i, peer, seq, i - first));
+                             q->cq[i], q->qscale[i], nullptr, idx->len, k_eff, k_eff, 1, q->res, i, peer, seq, i - first,
+                             use_floor ? floors[c] : nullptr, c == chunk - 1));
         // one query at a time: without the peer path its candidates are gathered and merged here
         if (sharded && !peer) LK_TRY(comm_gather_merge(idx->comm, idx, q->res, i, 1, k_eff));
     }
@@ -1040,6 +1064,21 @@ int lk_queries_fetch(lk_index *idx, lk_queries *q, int first, int count, int k, 
     LK_CUDA(cudaMemcpyAsync(q->res.host.p, q->res.dev.p, q->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
     LK_CUDA(cudaStreamSynchronize(idx->stream));
     const ResultArena &r = q->res;
+    // a query whose sampled floor turned out too high for this corpus came out short: once more without it
+    int repeated = 0;
+    for (int qi = first; qi < first + count && (size_t)qi < q->floored.size(); ++qi) {
+        if (!q->floored[(size_t)qi]) continue;
+        q->floored[(size_t)qi] = 0;
+        if (r.h_counts()[qi] < 0 || r.h_counts()[qi] >= r.k) continue;
+        if (repeated == 0) LK_TRY(ensure_scan_scratch(idx, r.k));  // (another search may have re-planned since)
+        LK_TRY(enqueue_query(idx, (const unsigned char *)q->d_query.p + (size_t)qi * idx->qbytes, q->centered != 0, q->cq[qi],
+                             q->qscale[qi], nullptr, idx->len, r.k, r.k, 1, q->res, qi));
+        ++repeated;
+    }
+    if (repeated > 0) {
+        LK_CUDA(cudaMemcpyAsync(q->res.host.p, q->res.dev.p, q->res.copy_bytes, cudaMemcpyDeviceToHost, idx->stream));
+        LK_CUDA(cudaStreamSynchronize(idx->stream));
+    }
     for (int i = 0; i < count; ++i) {
         const int qi = first + i;
         if (r.h_counts()[qi] < 0)

@@ -159,6 +159,7 @@ struct lk_queries {
     int centered = 0;
     lk::DevBuf d_query;
     std::vector<float> cq, qscale;
+    std::vector<char> floored;  // queries scanned with a sampled floor and not fetched since
     lk::ResultArena res;
 };
 

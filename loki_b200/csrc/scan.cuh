@@ -42,6 +42,10 @@ struct ScanArgs {
     // of the whole corpus exceed: each CTA then keeps a few dozen candidates instead of its own best k.
     // Should fewer than k hits come out after all, the caller repeats the scan without a floor.
     const unsigned long long *floor;
+    // 1 when the launch that wrote *floor may still be running as this one starts (it is the one just
+    // before on the stream): the kernel then waits for it before its first row.  0 when a launch in
+    // plain stream order lies between the two (a batch's sample scans are all issued first).
+    int floor_wait;
     unsigned long long *part;   // scratch [grid][k]: per-CTA candidate lists
     int *part_cnt;              // scratch [grid]: keys in each of them (nullptr: not recorded; the merge then searches)
     unsigned int *ticket;       // scratch: CTAs finished so far (self-resetting)

@@ -662,8 +662,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_bulk(const __grid_consta
     unsigned long long bound = ~0ull;
     if (a.bound != nullptr || a.floor != nullptr) {
         // a later pass of a large-k search (its bound is the previous pass's output) or a search with a
-        // sampled floor (the output of the sample scan launched just before): wait for that launch
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        // sampled floor that the launch just before has written: wait for that launch
+        if (a.bound != nullptr || a.floor_wait != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (a.bound != nullptr) bound = __ldcg(a.bound);
         if (a.floor != nullptr && tid == 0) buf.ctrl->thr = __ldcg(a.floor);
     }
@@ -886,7 +886,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_scan_wide(const __grid_consta
     TR::stage_query(qs, a.query != nullptr ? a.query : a.query_inline, a.chunks);
     unsigned long long bound = ~0ull;
     if (a.bound != nullptr || a.floor != nullptr) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (a.bound != nullptr || a.floor_wait != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (a.bound != nullptr) bound = __ldcg(a.bound);
         if (a.floor != nullptr && tid == 0) buf.ctrl->thr = __ldcg(a.floor);
     }

@@ -209,11 +209,18 @@ def test_large_k_scan_with_sampled_bound(lk, store, n, dim, k):
     queries = gaussian_rows(3, dim, 78 + k)
     if store == "i8":
         codes, _ = idx.read_rows()
+        idx.set_batch_mode(False)                             # (queries in one call as queued scans, not one product)
         both = idx.search(queries[:2], k)                     # two queries in one call
+        rq = idx.queries(queries)                             # and the three as queued scans on resident queries
+        rq.enqueue(0, 1, k)
+        rq.enqueue(1, 2, k)
+        qids, _, qisc, qcnt = rq.fetch(0, 3, k)
+        rq.close()
         for q in range(3):
             wid, wsc = _oracle_hits_i8(codes, queries[q], k)
             ids, _, isc, cnt = idx.search(queries[q], k)      # one synchronous call
             assert cnt[0] == k and np.array_equal(ids[0], wid) and np.array_equal(isc[0], wsc), f"query {q}"
+            assert qcnt[q] == k and np.array_equal(qids[q], wid) and np.array_equal(qisc[q], wsc), f"queued query {q}"
             if q < 2:
                 assert np.array_equal(both[0][q], wid) and np.array_equal(both[2][q], wsc)
     else:
@@ -246,6 +253,19 @@ def test_large_k_scan_when_the_sample_misleads(lk):
             wid, wsc = _oracle_hits_i8(codes, q, k)
             ids, _, isc, cnt = idx.search(q, k)
             assert cnt[0] == k and np.array_equal(ids[0], wid) and np.array_equal(isc[0], wsc)
+            # the same through the two multi-query forms: one call with three queries (the middle one is
+            # an ordinary query, which keeps its sampled bound), and queued scans on resident queries
+            other = gaussian_rows(1, dim, 5152)[0]
+            trio = np.stack([q, other, q])
+            oid, osc = _oracle_hits_i8(codes, other, k)
+            ids3, _, isc3, cnt3 = idx.search(trio, k)
+            rq = idx.queries(trio)
+            rq.enqueue(0, 3, k)
+            qid3, _, qisc3, qcnt3 = rq.fetch(0, 3, k)
+            rq.close()
+            for j, (w_i, w_s) in enumerate([(wid, wsc), (oid, osc), (wid, wsc)]):
+                assert cnt3[j] == k and np.array_equal(ids3[j], w_i) and np.array_equal(isc3[j], w_s), f"batch {j}"
+                assert qcnt3[j] == k and np.array_equal(qid3[j], w_i) and np.array_equal(qisc3[j], w_s), f"queued {j}"
         else:
             sc = O.scan_f32(idx.read_rows(), O.normalize(q), workers=CORES)
             got = idx.search(q, k)
