@@ -40,7 +40,12 @@ __device__ __forceinline__ void ptile_from_linear(long long t, int *bi, int *bj)
 __global__ void __launch_bounds__(PTHREADS) k_prescreen_pairs(const float *__restrict__ v, int n, int dim, int ld,
                                                               float threshold, long long n_tiles,
                                                               int *__restrict__ near, int *__restrict__ count) {
-    __shared__ float As[PT][PK + 4], Bs[PT][PK + 4];  // +4: rows 80 B apart, 16-byte aligned, conflict-free
+    // +4: rows lie 80 B = 5 x 16 B apart.  A thread's four columns are rows tx, tx+16, tx+32, tx+48 of Bs,
+    // so the eight lanes of a quarter warp read eight neighbouring rows, which fall on eight different
+    // 16-byte bank groups (four neighbouring rows per thread would put them on two).
+    // Two copies of each tile: while the threads compute on one, the next step's floats go into the other,
+    // which leaves one barrier per step.
+    __shared__ float As[2][PT][PK + 4], Bs[2][PT][PK + 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int dim4 = dim & ~3;
     for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
@@ -62,11 +67,11 @@ __global__ void __launch_bounds__(PTHREADS) k_prescreen_pairs(const float *__res
         const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
         float4 a_next = (ap && lkk < ld) ? *reinterpret_cast<const float4 *>(ap) : zero4;
         float4 b_next = (bp && lkk < ld) ? *reinterpret_cast<const float4 *>(bp) : zero4;
-        for (int k0 = 0; k0 < dim; k0 += PK) {
-            __syncthreads();
-            *reinterpret_cast<float4 *>(&As[lrow][lkk]) = a_next;
-            *reinterpret_cast<float4 *>(&Bs[lrow][lkk]) = b_next;
-            __syncthreads();
+        // (every step of the tile before ended in a barrier: nobody still reads copy 0)
+        *reinterpret_cast<float4 *>(&As[0][lrow][lkk]) = a_next;
+        *reinterpret_cast<float4 *>(&Bs[0][lrow][lkk]) = b_next;
+        __syncthreads();
+        for (int k0 = 0, cur = 0; k0 < dim; k0 += PK, cur ^= 1) {
             {
                 const int kn = k0 + PK + lkk;
                 a_next = (ap && kn < ld) ? *reinterpret_cast<const float4 *>(ap + k0 + PK) : zero4;
@@ -77,9 +82,9 @@ __global__ void __launch_bounds__(PTHREADS) k_prescreen_pairs(const float *__res
                 if (k0 + g >= dim) break;
                 float4 a[4], b[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4 *>(&As[ty * 4 + r][g]);
+                for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4 *>(&As[cur][ty * 4 + r][g]);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const float4 *>(&Bs[tx * 4 + c][g]);
+                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const float4 *>(&Bs[cur][tx + 16 * c][g]);
                 if (k0 + g < dim4) {  // a full group of four: element m feeds accumulator m
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
@@ -102,13 +107,17 @@ __global__ void __launch_bounds__(PTHREADS) k_prescreen_pairs(const float *__res
                         }
                 }
             }
+            // the other copy was last read one step ago, before that step's barrier
+            *reinterpret_cast<float4 *>(&As[cur ^ 1][lrow][lkk]) = a_next;
+            *reinterpret_cast<float4 *>(&Bs[cur ^ 1][lrow][lkk]) = b_next;
+            __syncthreads();
         }
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const int i = i0 + ty * 4 + r;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int j = j0 + tx * 4 + c;
+                const int j = j0 + tx + 16 * c;
                 const float s = __fadd_rn(__fadd_rn(acc[r][c][0], acc[r][c][1]), __fadd_rn(acc[r][c][2], acc[r][c][3]));
                 if (i < n && j < i && s >= threshold) {
                     const int pos = atomicAdd(&count[i], 1);

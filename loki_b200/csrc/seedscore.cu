@@ -47,7 +47,12 @@ __global__ void __launch_bounds__(STHREADS) k_seed_scores_grouped(const float *_
                                                                   float min_score, SeedHit *__restrict__ hits,
                                                                   unsigned long long cap,
                                                                   unsigned long long *__restrict__ n_hits) {
-    __shared__ float As[ST][SK + 4], Bs[ST][SK + 4];  // +4: rows 80 B apart, 16-byte aligned, conflict-free
+    // +4: rows lie 80 B = 5 x 16 B apart.  A thread's four columns are rows tx, tx+16, tx+32, tx+48 of Bs,
+    // so the eight lanes of a quarter warp read eight neighbouring rows, which fall on eight different
+    // 16-byte bank groups (four neighbouring rows per thread would put them on two).
+    // Two copies of each tile: while the threads compute on one, the next step's floats go into the other,
+    // which leaves one barrier per step.
+    __shared__ float As[2][ST][SK + 4], Bs[2][ST][SK + 4];
     __shared__ int s_base[ST / 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int g_tiles = (n_groups + ST / 4 - 1) / (ST / 4), s_tiles = (n_seeds + ST - 1) / ST;
@@ -71,11 +76,11 @@ __global__ void __launch_bounds__(STHREADS) k_seed_scores_grouped(const float *_
         const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
         float4 a_next = (ap && lkk < ld) ? *reinterpret_cast<const float4 *>(ap) : zero4;
         float4 b_next = (bp && lkk < ld) ? *reinterpret_cast<const float4 *>(bp) : zero4;
-        for (int k0 = 0; k0 < ld; k0 += SK) {
-            __syncthreads();
-            *reinterpret_cast<float4 *>(&As[lrow][lkk]) = a_next;
-            *reinterpret_cast<float4 *>(&Bs[lrow][lkk]) = b_next;
-            __syncthreads();
+        // (every step of the tile before ended in a barrier: nobody still reads copy 0)
+        *reinterpret_cast<float4 *>(&As[0][lrow][lkk]) = a_next;
+        *reinterpret_cast<float4 *>(&Bs[0][lrow][lkk]) = b_next;
+        __syncthreads();
+        for (int k0 = 0, cur = 0; k0 < ld; k0 += SK, cur ^= 1) {
             {
                 const int kn = k0 + SK + lkk;
                 a_next = (ap && kn < ld) ? *reinterpret_cast<const float4 *>(ap + k0 + SK) : zero4;
@@ -86,9 +91,9 @@ __global__ void __launch_bounds__(STHREADS) k_seed_scores_grouped(const float *_
                 if (k0 + g >= ld) break;
                 float4 a[4], b[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4 *>(&As[ty * 4 + r][g]);
+                for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4 *>(&As[cur][ty * 4 + r][g]);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const float4 *>(&Bs[tx * 4 + c][g]);
+                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const float4 *>(&Bs[cur][tx + 16 * c][g]);
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
 #pragma unroll
@@ -99,6 +104,10 @@ __global__ void __launch_bounds__(STHREADS) k_seed_scores_grouped(const float *_
                         tt[r][c] = __fadd_rn(tt[r][c], __fmul_rn(a[r].w, b[c].w));
                     }
             }
+            // the other copy was last read one step ago, before that step's barrier
+            *reinterpret_cast<float4 *>(&As[cur ^ 1][lrow][lkk]) = a_next;
+            *reinterpret_cast<float4 *>(&Bs[cur ^ 1][lrow][lkk]) = b_next;
+            __syncthreads();
         }
         const int base = s_base[ty];
         if (base < 0) continue;
@@ -106,7 +115,7 @@ __global__ void __launch_bounds__(STHREADS) k_seed_scores_grouped(const float *_
         for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int j = j0 + tx * 4 + c;
+                const int j = j0 + tx + 16 * c;
                 const float sc = __fadd_rn(s[r][c], tt[r][c]);
                 if (j < n_seeds && sc >= min_score) {
                     const unsigned long long pos = atomicAdd(n_hits, 1ull);
