@@ -242,16 +242,37 @@ static bool floor_applies(const lk_index *idx, bool filtered, bool sharded, int 
            idx->len >= 64ll * k_eff && idx->len >= 4ll * kSampleMin;
 }
 
+// Rows in the sample of the index as it stands, and the rank of the sample's key that serves as the bound.
+static int sample_rows(const lk_index *idx) {
+    return (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 64)) & ~31;
+}
+static int sample_rank(const lk_index *idx, int k_eff, int S) {
+    const double r = (double)k_eff * S / (double)idx->len;
+    const double x = (5.0 + std::sqrt(25.0 + 4.0 * r)) * 0.5;  // r' - 5 sqrt(r') >= r
+    return std::min<int>(kMaxK, std::max<int>(16, (int)std::ceil(x * x)));
+}
+// The sample's slots at the head of d_sample (of at least `bytes`), refilled when the buffer or the index changed.
+static int sample_slots(lk_index *idx, int S, size_t bytes) {
+    const void *before = idx->d_sample.p;
+    LK_TRY(idx->d_sample.reserve(bytes));
+    if (idx->d_sample.p != before || idx->sample_len != idx->len || idx->sample_n != S) {
+        k_fill_stride<<<64, 256, 0, idx->stream>>>((int *)idx->d_sample.p, S, idx->len);
+        LK_CUDA(cudaGetLastError());
+        idx->sample_len = idx->len;
+        idx->sample_n = S;
+        idx->aux_launches++;
+    }
+    return 0;
+}
+
 // Enqueue the sample scan of one prepared query (in device memory, or inline in `inl`); *floor_out
 // receives the device address of the bound.  A batch issues the sample scans of up to kFloorChunk
 // queries first (`blocks` of them, this one writing output block `block`) and the real scans after
 // them: the real scans then follow one another directly and overlap at their edges.
 static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const unsigned char *inl, bool centered, float cq,
                                float qscale, int k_eff, const unsigned long long **floor_out, int block = 0, int blocks = 1) {
-    const int S = (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 64)) & ~31;
-    const double r = (double)k_eff * S / (double)idx->len;
-    const double x = (5.0 + std::sqrt(25.0 + 4.0 * r)) * 0.5;  // r' - 5 sqrt(r') >= r
-    const int rr = std::min<int>(kMaxK, std::max<int>(16, (int)std::ceil(x * x)));
+    const int S = sample_rows(idx);
+    const int rr = sample_rank(idx, k_eff, S);
     if (idx->plan_sample_k != rr) {
         LK_TRY(scan_plan(idx->type, idx->chunks, rr, idx->device, &idx->plan_sample));
         idx->plan_sample_k = rr;
@@ -260,15 +281,7 @@ static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const un
     const size_t block_bytes = (size_t)round_up((int64_t)rr * 24 + 16, 256);
     const size_t o_keys = (size_t)round_up((int64_t)S * 4, 256) + (size_t)block * block_bytes, o_ids = o_keys + (size_t)rr * 8;
     const size_t o_sc = o_ids + (size_t)rr * 8, o_isc = o_sc + (size_t)rr * 4, o_cnt = o_isc + (size_t)rr * 4;
-    const void *before = idx->d_sample.p;
-    LK_TRY(idx->d_sample.reserve((size_t)round_up((int64_t)S * 4, 256) + (size_t)std::max(blocks, block + 1) * block_bytes));
-    if (idx->d_sample.p != before || idx->sample_len != idx->len || idx->sample_n != S) {
-        k_fill_stride<<<64, 256, 0, idx->stream>>>((int *)idx->d_sample.p, S, idx->len);
-        LK_CUDA(cudaGetLastError());
-        idx->sample_len = idx->len;
-        idx->sample_n = S;
-        idx->aux_launches++;
-    }
+    LK_TRY(sample_slots(idx, S, (size_t)round_up((int64_t)S * 4, 256) + (size_t)std::max(blocks, block + 1) * block_bytes));
     LK_TRY(idx->part.reserve((size_t)scan_max_grid(idx->plan_sample) * rr * 8 + kPartCntBytes));
     unsigned char *b = (unsigned char *)idx->d_sample.p;
     ScanArgs a = base_args(idx, centered, cq, qscale, (const int *)b, S, rr);
@@ -916,7 +929,7 @@ int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npo
     const int grid = shared_scan_grid(T, idx->chunks, k_pass, idx->device, &err);
     if (err == -1) return fail(LK_ERANGE, "lk_search_shared: terms x dim too large for shared memory");
     if (err != 0 || grid <= 0) return fail(LK_ECUDA, std::string("shared scan occupancy query: ") + cudaGetErrorString((cudaError_t)err));
-    LK_TRY(idx->part.reserve((size_t)grid * k_pass * 8));
+    LK_TRY(idx->part.reserve((size_t)grid * k_pass * 8 + kPartCntBytes));
     LK_TRY(idx->res.shape(1, k_eff, passes));
     // upload: terms padded to the row width, then the scalar block
     const size_t ldf = (size_t)idx->ld / 4;
@@ -947,6 +960,47 @@ int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npo
         LK_CUDA(cudaMemcpyAsync(idx->d_slots.p, allow_slots, (size_t)n_cand * 4, cudaMemcpyHostToDevice, idx->stream));
         d_slots = (const int *)idx->d_slots.p;
     }
+    // Large k: a sample scan first, whose r-th best key bounds the scan from below (see enqueue_sample_scan;
+    // the same sample slots, the gathered kernel for the sample, plain stream order between the two launches).
+    const bool use_floor = floor_applies(idx, filtered, false, k_eff, passes);
+    const unsigned long long *floor = nullptr;
+    if (use_floor) {
+        const int S = sample_rows(idx);
+        const int rr = sample_rank(idx, k_eff, S);
+        int serr = 0;
+        const int sgrid = shared_scan_grid(T, idx->chunks, rr, idx->device, &serr);
+        if (serr != 0 || sgrid <= 0) return fail(LK_ECUDA, "shared scan occupancy query (sample)");
+        LK_TRY(idx->part.reserve((size_t)std::max(grid * k_pass, sgrid * rr) * 8 + kPartCntBytes));
+        const size_t o_keys = (size_t)round_up((int64_t)S * 4, 256), o_ids = o_keys + (size_t)rr * 8, o_sc = o_ids + (size_t)rr * 8;
+        const size_t o_cnt = o_sc + (size_t)rr * 4;
+        LK_TRY(sample_slots(idx, S, o_cnt + 16));
+        unsigned char *b = (unsigned char *)idx->d_sample.p;
+        SharedArgs sa;
+        sa.rows = idx->d_rows;
+        sa.ld = idx->ld;
+        sa.chunks = idx->chunks;
+        sa.n = S;
+        sa.slots = (const int *)b;
+        sa.terms = (const float *)idx->d_query.p;
+        sa.params = (const SharedParams *)((const unsigned char *)idx->d_query.p + par_off);
+        sa.cnorm = centered ? idx->d_cnorm : nullptr;
+        sa.mu = idx->d_mu;
+        sa.k = rr;
+        sa.bound = nullptr;
+        sa.floor = nullptr;
+        sa.part = (unsigned long long *)idx->part.p;
+        sa.part_cnt = (int *)((unsigned char *)idx->part.p + idx->part.bytes - kPartCntBytes);
+        sa.ticket = idx->d_ticket;
+        sa.out_keys = (unsigned long long *)(b + o_keys);
+        sa.out_ids = (long long *)(b + o_ids);
+        sa.out_scores = (float *)(b + o_sc);
+        sa.out_iscores = nullptr;
+        sa.out_count = (int *)(b + o_cnt);
+        sa.shard_base = idx->shard_base;
+        LK_TRY(shared_scan_launch(sa, T, sgrid, idx->stream));
+        idx->scan_launches++;
+        floor = (const unsigned long long *)(b + o_keys) + (rr - 1);
+    }
     for (int p = 0; p < passes; ++p) {
         const int done = p * kMaxK;
         SharedArgs a;
@@ -961,7 +1015,9 @@ int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npo
         a.mu = idx->d_mu;
         a.k = std::min(kMaxK, k_eff - done);
         a.bound = (p == 0) ? nullptr : idx->res.d_keys() + done - 1;
+        a.floor = floor;
         a.part = (unsigned long long *)idx->part.p;
+        a.part_cnt = (int *)((unsigned char *)idx->part.p + idx->part.bytes - kPartCntBytes);
         a.ticket = idx->d_ticket;
         a.out_keys = idx->res.d_keys() + done;
         a.out_ids = idx->res.d_ids() + done;
@@ -976,6 +1032,13 @@ int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npo
     LK_CUDA(cudaStreamSynchronize(idx->stream));
     int32_t cnt = 0;
     LK_TRY(unpack_results(idx->res, 1, k, k_eff, passes, out_ids, out_scores, nullptr, &cnt));
+    if (use_floor && cnt < k_eff) {  // the sampled bound was too high for this corpus: once more without it
+        idx->no_floor = true;
+        const int st = lk_search_shared(idx, pos, posw, npos, neg, negw, nneg, beta, lambda, k, scoring, allow_slots, n_allow,
+                                        out_ids, out_scores, out_count);
+        idx->no_floor = false;
+        return st;
+    }
     *out_count = cnt;
     return LK_OK;
 }

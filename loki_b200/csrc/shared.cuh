@@ -24,7 +24,9 @@ struct SharedArgs {
     const float *mu;             // [ld/4] mean vector, zero padded (centered only)
     int k;
     const unsigned long long *bound;
+    const unsigned long long *floor;  // nullptr, or an exclusive lower bound for the keys (ScanArgs::floor)
     unsigned long long *part;
+    int *part_cnt;               // nullptr, or [grid]: how many keys each CTA's list holds
     unsigned int *ticket;
     unsigned long long *out_keys;
     long long *out_ids;

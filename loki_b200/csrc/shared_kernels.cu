@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_scan_shared(const SharedArg
     if (tid == 0) {
         buf.ctrl->count = 0;
         buf.ctrl->n_done = 0;
-        buf.ctrl->thr = 0ull;
+        buf.ctrl->thr = a.floor ? __ldcg(a.floor) : 0ull;
     }
     // terms -> float64, two planes per term (elements 0,1 / 2,3 of each chunk)
     for (int i = tid; i < T * a.chunks; i += kScanThreads) {

@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32, 1) k_scan_shared_mma(const 
     if (tid == 0) {
         buf.ctrl->count = 0;
         buf.ctrl->n_done = 0;
-        buf.ctrl->thr = 0ull;
+        buf.ctrl->thr = a.floor ? __ldcg(a.floor) : 0ull;
     }
     {   // scalars, terms (plus a row of zeros) and the mean into shared memory
         const int c16 = (int)(a.ld / 16);
@@ -329,6 +329,7 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32, 1) k_scan_shared_mma(const 
 
     unsigned long long *mine = a.part + (size_t)blockIdx.x * a.k;
     for (int i = tid; i < a.k; i += n_threads) mine[i] = buf.keys[i];
+    if (tid == 0 && a.part_cnt != nullptr) a.part_cnt[blockIdx.x] = min(buf.ctrl->count, a.k);
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -339,7 +340,20 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32, 1) k_scan_shared_mma(const 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    cand_select_from_lists(buf, a.part, (int)gridDim.x);
+    // The last CTA merges all lists.  Its slice buffers are idle now and hold more keys than its own
+    // candidate buffer: the keys above the merge's starting threshold (between k and a few k) then fit
+    // in one pass; should they not, the bisecting merge starts over.
+    {
+        const int spare_keys = (int)(((size_t)n_warps * nbuf * kMmaRows * pitch) / 8);
+        int want = buf.cap;
+        while (want < 4 * a.k && want * 2 <= spare_keys) want <<= 1;
+        if (want > buf.cap) {
+            buf.keys = reinterpret_cast<unsigned long long *>(smem + L.bufs);
+            buf.cap = want;
+            buf.limit = want - kMmaOfferSlack;
+        }
+    }
+    if (!cand_select_flat(buf, a.part, a.part_cnt, (int)gridDim.x)) cand_select_from_lists(buf, a.part, (int)gridDim.x);
     const int cnt = buf.ctrl->count;
     for (int i = tid; i < a.k; i += n_threads) {
         const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;

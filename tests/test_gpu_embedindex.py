@@ -149,6 +149,30 @@ def _shared_large_case(lk, n, dim, k, npos, nneg):
     assert np.all(np.diff(scores) <= 0)
 
 
+@pytest.mark.parametrize("mislead", [False, True])
+def test_shared_search_large_k_with_sampled_bound(lk, mislead):
+    """k of 256 and more on a large index: a sample of the rows is scored first and bounds the scan from
+    below.  With `mislead` every sampled row is a near-copy of the first positive and no other row is, so
+    the bound lies above almost the whole index, too few rows pass, and the search must run again."""
+    n, dim, k = 163_840, 128, 1000                # the sample of an index of this size: every 20th row
+    rows = _common_rows(n, dim, 71)
+    pos = _common_rows(2, dim, 72)
+    if mislead:
+        rng = np.random.default_rng(73)
+        rows[::20] = pos[0] + 0.05 * rng.standard_normal((n // 20, dim)).astype(np.float32)
+    rows = np.stack([O.normalize(v) for v in rows])
+    idx = lk.DeviceIndex(dim, lk.LK_F32)
+    idx.append(rows)
+    stored = idx.read_rows(0, n)
+    ids, scores = idx.search_shared(pos, k=k, scoring=lk.LK_SCORE_PLAIN)
+    want = O.SharedQuery([O.normalize(p) for p in pos], None, None, None).scan(stored)
+    order = np.lexsort((np.arange(n), -want.astype(np.float64)))[:k]
+    assert len(ids) == k and len(set(ids.tolist())) == k
+    np.testing.assert_allclose(scores, want[order], rtol=2e-5, atol=1e-6)
+    np.testing.assert_allclose(scores, want[ids], rtol=2e-5, atol=1e-6)
+    idx.close()
+
+
 def test_shared_search_large_centered_index_matches_oracle(impl):
     n, dim, k = 8200, 64, 30
     rows = _common_rows(n, dim, 61)
