@@ -223,8 +223,8 @@ static ScanArgs base_args(lk_index *idx, bool centered, float cq, float qscale, 
 // part of the corpus; for k = 1,000 on 148 CTAs that is 148,000 keys kept, cut and merged to
 // find 1,000.  Instead, a strided sample of S rows is scanned first (a gathered scan, a few
 // microseconds); the sample's r-th best key becomes an exclusive lower bound for the real
-// scan.  r is chosen so that the expected number of corpus rows above the bound is about
-// 2k and k lies five standard deviations below it: each CTA then keeps a few dozen keys.
+// scan.  r is chosen so that k lies four standard deviations below the expected number of corpus
+// rows above the bound (a few k): each CTA then keeps a few dozen keys.
 // If fewer than k hits come out after all (a sample that misrepresents the corpus), the
 // caller repeats the scan without the bound, so the result is exact either way.
 // ---------------------------------------------------------------------------
@@ -243,12 +243,14 @@ static bool floor_applies(const lk_index *idx, bool filtered, bool sharded, int 
 }
 
 // Rows in the sample of the index as it stands, and the rank of the sample's key that serves as the bound.
-static int sample_rows(const lk_index *idx) {
-    return (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, idx->len / 64)) & ~31;
+static int sample_rows(const lk_index *idx, int k_eff) {
+    // about 8 of the k best rows fall into the sample: the bound's rank then stays within 32, where a
+    // scan keeps its candidates in registers and merges without a sort
+    return (int)std::min<long long>(kSampleMax, std::max<long long>(kSampleMin, 8 * idx->len / k_eff)) & ~31;
 }
 static int sample_rank(const lk_index *idx, int k_eff, int S) {
     const double r = (double)k_eff * S / (double)idx->len;
-    const double x = (5.0 + std::sqrt(25.0 + 4.0 * r)) * 0.5;  // r' - 5 sqrt(r') >= r
+    const double x = (4.0 + std::sqrt(16.0 + 4.0 * r)) * 0.5;  // r' - 4 sqrt(r') >= r
     return std::min<int>(kMaxK, std::max<int>(16, (int)std::ceil(x * x)));
 }
 // The sample's slots at the head of d_sample (of at least `bytes`), refilled when the buffer or the index changed.
@@ -271,7 +273,7 @@ static int sample_slots(lk_index *idx, int S, size_t bytes) {
 // them: the real scans then follow one another directly and overlap at their edges.
 static int enqueue_sample_scan(lk_index *idx, const unsigned char *d_q, const unsigned char *inl, bool centered, float cq,
                                float qscale, int k_eff, const unsigned long long **floor_out, int block = 0, int blocks = 1) {
-    const int S = sample_rows(idx);
+    const int S = sample_rows(idx, k_eff);
     const int rr = sample_rank(idx, k_eff, S);
     if (idx->plan_sample_k != rr) {
         LK_TRY(scan_plan(idx->type, idx->chunks, rr, idx->device, &idx->plan_sample));
@@ -965,7 +967,7 @@ int lk_search_shared(lk_index *idx, const float *pos, const float *posw, int npo
     const bool use_floor = floor_applies(idx, filtered, false, k_eff, passes);
     const unsigned long long *floor = nullptr;
     if (use_floor) {
-        const int S = sample_rows(idx);
+        const int S = sample_rows(idx, k_eff);
         const int rr = sample_rank(idx, k_eff, S);
         int serr = 0;
         const int sgrid = shared_scan_grid(T, idx->chunks, rr, idx->device, &serr);

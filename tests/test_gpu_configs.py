@@ -241,9 +241,10 @@ def test_large_k_scan_when_the_sample_misleads(lk):
     n, dim, k = 524_288, 64, 400
     rows = gaussian_rows(n, dim, 5150)
     q = gaussian_rows(1, dim, 5151)[0]
-    stride = 64                                   # the sample takes every 64th row of an index of this size
+    s_rows = min(32768, max(8192, 8 * n // k)) & ~31      # the library's sample of an index of this size for this k
+    sample = np.arange(s_rows, dtype=np.int64) * n // s_rows
     rng = np.random.default_rng(5)
-    rows[::stride] = q + 0.05 * rng.standard_normal((n // stride, dim)).astype(np.float32)
+    rows[sample] = q + 0.05 * rng.standard_normal((s_rows, dim)).astype(np.float32)
     for store in (lk.LK_I8, lk.LK_F32):
         idx = lk.DeviceIndex(dim, store)
         idx.append(rows)
