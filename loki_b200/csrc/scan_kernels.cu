@@ -301,8 +301,33 @@ __device__ __forceinline__ int peer_merge_emit(const PeerTable &pt, unsigned seq
     __syncthreads();
     const bool bad = s_peer_bad != 0;
     const PeerInbox *mine_in = pt.inbox[pt.rank];
-    cand_select_from_lists(buf, &mine_in->keys[slot][0][0], pt.world, kPeerMaxK);
-    const int cnt = buf.ctrl->count;
+    // When all ranks' lists fit twice into the buffer (a top-10 of 8 ranks: 80 keys) they are fetched in one
+    // round trip, sorted in the lower half and kept as they came in the upper half, where the owner of
+    // every hit is then found without further trips to memory.  Larger merges take the streaming path.
+    const int total = pt.world * k, half = buf.cap >> 1;
+    const bool local = total <= half;
+    const unsigned long long *lists = buf.keys + half;  // [world][k], as delivered
+    __shared__ int s_peer_cnt;
+    if (local) {
+        for (int i = tid; i < half; i += T) {
+            const unsigned long long v = (i < total) ? __ldcg(&mine_in->keys[slot][i / k][i % k]) : 0ull;
+            buf.keys[i] = v;
+            buf.keys[half + i] = v;
+        }
+        if (tid == 0) {
+            buf.ctrl->count = total;
+            buf.ctrl->thr = 0ull;
+            s_peer_cnt = 0;
+        }
+        __syncthreads();
+        cand_prune(buf);  // ranked, best k kept (empty entries are 0 and sort last)
+        for (int i = tid; i < k; i += T)
+            if (buf.keys[i] != 0ull && (i + 1 == k || buf.keys[i + 1] == 0ull)) s_peer_cnt = i + 1;
+        __syncthreads();
+    } else {
+        cand_select_from_lists(buf, &mine_in->keys[slot][0][0], pt.world, kPeerMaxK);
+    }
+    const int cnt = local ? s_peer_cnt : buf.ctrl->count;
     for (int i = tid; i < k; i += T) {
         const unsigned long long key = (i < cnt) ? buf.keys[i] : 0ull;
         if (key == 0ull) {
@@ -322,7 +347,7 @@ __device__ __forceinline__ int peer_merge_emit(const PeerTable &pt, unsigned seq
             int lo = 0, hi = k - 1;
             while (lo <= hi) {  // ranked descending
                 const int mid = (lo + hi) >> 1;
-                const unsigned long long v = __ldcg(&mine_in->keys[slot][r][mid]);
+                const unsigned long long v = local ? lists[r * k + mid] : __ldcg(&mine_in->keys[slot][r][mid]);
                 if (v == key) {
                     sc = __ldcg(&mine_in->payload[slot][r][mid]);
                     found = true;
@@ -412,10 +437,20 @@ __device__ __forceinline__ void publish_and_finish(const ScanArgs &a, const Cand
             unsigned int *f = &pt.inbox[tid]->flags[slot][pt.rank];
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tag) : "memory");
         }
+        // (the ranks' lists are merged in the idle stage buffers too when they do not fit twice into `buf`;
+        //  all threads are past their reads of `buf`: the barrier above)
+        CandBuf pbuf = buf;
+        if (spare != nullptr && 2 * pt.world * a.k > pbuf.cap) {
+            int want = pbuf.cap;
+            while (want < 2 * pt.world * a.k && want * 2 <= spare_keys) want <<= 1;
+            pbuf.keys = spare;
+            pbuf.cap = want;
+            pbuf.limit = want - kScanThreads;
+        }
         if (a.defer == 0) {
-            cnt = peer_merge_emit<TYPE>(pt, a.seq, a.k, buf, a.out_ids, a.out_scores, a.out_iscores);
+            cnt = peer_merge_emit<TYPE>(pt, a.seq, a.k, pbuf, a.out_ids, a.out_scores, a.out_iscores);
         } else if (a.d_out_ids != nullptr) {
-            cnt = peer_merge_emit<TYPE>(pt, a.seq - (unsigned)a.defer, a.k, buf, a.d_out_ids, a.d_out_scores, a.d_out_iscores);
+            cnt = peer_merge_emit<TYPE>(pt, a.seq - (unsigned)a.defer, a.k, pbuf, a.d_out_ids, a.d_out_scores, a.d_out_iscores);
             count_to = a.d_out_count;
         } else {
             count_to = nullptr;  // merged later, by a following launch or the drain
