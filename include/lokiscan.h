@@ -131,7 +131,11 @@ LK_API int lk_index_center_state(lk_index *idx, int *live, int64_t *n_centered, 
  * key is the raw int32 dot).  A centered index re-centres first when it has
  * drifted (media-server/embedindex/embedindex.go:234-268), so this call may mutate.
  * With a communicator attached (lk_index_attach_comm) every rank must call with
- * the same queries and k and receives the merged global result. */
+ * the same queries and k and receives the merged global result.
+ * For k of 256 and more on an unsharded, unfiltered index of 64k+ rows the call scans a
+ * sample of the rows first and uses its result as a lower bound for the scan; a query for
+ * which that bound lets fewer than k rows through is scanned again without it, so the hits
+ * are the exact top k in every case (lk_search_shared does the same). */
 LK_API int lk_search(lk_index *idx, const float *queries, int nq, int k, int scoring,
                      const int32_t *allow_slots, int64_t n_allow,
                      int64_t *out_ids, float *out_scores, int32_t *out_iscores,
@@ -190,9 +194,14 @@ LK_API int lk_queries_create(lk_index *idx, const float *queries, int nq, int sc
                              lk_queries **out);
 LK_API int lk_queries_destroy(lk_queries *q);
 /* Enqueue one scan per query [first, first+count) on the index's stream, no host
- * synchronisation; results stay on the device until lk_queries_fetch. */
+ * synchronisation; results stay on the device until lk_queries_fetch.  With k of 256 and
+ * more on a large index every query is first scanned over a sample of the rows, whose result
+ * bounds the real scan from below (the sample scans of up to 64 queries are issued together,
+ * ahead of their scans). */
 LK_API int lk_search_resident(lk_index *idx, lk_queries *q, int first, int count, int k);
-/* Wait for the stream and copy the results of queries [first, first+count) out. */
+/* Wait for the stream and copy the results of queries [first, first+count) out.  A query
+ * whose sampled bound let fewer than k rows through is scanned again here, without the bound,
+ * before its result is returned: results are exact either way. */
 LK_API int lk_queries_fetch(lk_index *idx, lk_queries *q, int first, int count, int k,
                             int64_t *out_ids, float *out_scores, int32_t *out_iscores,
                             int32_t *out_counts);
