@@ -320,9 +320,22 @@ __device__ __forceinline__ int peer_merge_emit(const PeerTable &pt, unsigned seq
             s_peer_cnt = 0;
         }
         __syncthreads();
-        cand_prune(buf);  // ranked, best k kept (empty entries are 0 and sort last)
-        for (int i = tid; i < k; i += T)
-            if (buf.keys[i] != 0ull && (i + 1 == k || buf.keys[i + 1] == 0ull)) s_peer_cnt = i + 1;
+        if (total <= T) {
+            // a key per thread: its place is the number of keys above it (keys are distinct; 80 compares
+            // against shared memory instead of a sorting network that this CTA runs once, from cold code)
+            const unsigned long long mine = (tid < total) ? lists[tid] : 0ull;
+            int above = 0;
+            for (int j = 0; j < total; ++j) above += (lists[j] > mine) ? 1 : 0;
+            const int present = __syncthreads_count(mine != 0ull);
+            for (int i = tid; i < half; i += T) buf.keys[i] = 0ull;
+            __syncthreads();
+            if (mine != 0ull && above < k) buf.keys[above] = mine;
+            if (tid == 0) s_peer_cnt = min(present, k);
+        } else {
+            cand_prune(buf);  // ranked, best k kept (empty entries are 0 and sort last)
+            for (int i = tid; i < k; i += T)
+                if (buf.keys[i] != 0ull && (i + 1 == k || buf.keys[i + 1] == 0ull)) s_peer_cnt = i + 1;
+        }
         __syncthreads();
     } else {
         cand_select_from_lists(buf, &mine_in->keys[slot][0][0], pt.world, kPeerMaxK);
