@@ -144,33 +144,67 @@ __device__ __noinline__ inline void block_sort_desc(unsigned long long *keys, in
     }
 }
 
+// cand_prune for up to 32 R keys, by one warp: key i sits in register i / 32 of lane i % 32.  A bitonic
+// network: partners up to 16 apart meet through shuffles, partners 32 and 64 apart in the lane's own
+// registers.  Keeps the best k, zeroes the rest, raises the threshold.
+template <int R>
+__device__ __forceinline__ void warp_sort_prune(const CandBuf &b, int c, int lane) {
+    unsigned long long v[R];
+#pragma unroll
+    for (int e = 0; e < R; ++e) v[e] = (e * 32 + lane < c) ? b.keys[e * 32 + lane] : 0ull;
+#pragma unroll
+    for (int size = 2; size <= 32 * R; size <<= 1) {
+#pragma unroll
+        for (int rs = R / 2; rs > 0; rs >>= 1) {  // strides of 32 rs keys: inside the lane
+            if (32 * rs >= size) continue;
+#pragma unroll
+            for (int e = 0; e < R; ++e) {
+                if ((e & rs) != 0) continue;
+                const bool desc = ((e * 32) & size) == 0;
+                const unsigned long long x = v[e], y = v[e + rs];
+                const bool sw = (x < y) == desc;
+                v[e] = sw ? y : x;
+                v[e + rs] = sw ? x : y;
+            }
+        }
+#pragma unroll
+        for (int stride = 16; stride > 0; stride >>= 1) {
+            if (stride >= size) continue;
+            const bool lower = (lane & stride) == 0;
+#pragma unroll
+            for (int e = 0; e < R; ++e) {
+                const bool desc = ((e * 32 + lane) & size) == 0;
+                const unsigned long long o = shfl_xor_u64(v[e], stride);
+                v[e] = ((v[e] > o) == (lower == desc)) ? v[e] : o;  // the lower lane of a descending pair keeps the larger key
+            }
+        }
+    }
+    const int keep = c < b.k ? c : b.k;
+    unsigned long long kth = 0ull;
+#pragma unroll
+    for (int e = 0; e < R; ++e) {
+        b.keys[e * 32 + lane] = (e * 32 + lane < keep) ? v[e] : 0ull;
+        const unsigned long long at = shfl_u64(v[e], (b.k - 1) & 31);  // the k-th key, when there are k
+        if (((b.k - 1) >> 5) == e) kth = at;
+    }
+    if (lane == 0) {
+        b.ctrl->count = keep;
+        if (keep == b.k && kth > b.ctrl->thr) b.ctrl->thr = kth;  // only ever rises
+    }
+}
+
 // Sort keys[0..count) descending, keep the best k, zero the rest, raise thr.
 // Must be called by all threads of the CTA with `count` stable.
 __device__ inline void cand_prune(const CandBuf &b) {
     const int tid = threadIdx.x, T = blockDim.x;
     const int c = b.ctrl->count;
-    if (c <= 32) {
-        // few keys: one warp sorts them in registers (a bitonic network over the lanes), no barriers
+    if (c <= 128) {
+        // few keys (a CTA's warps handing over their registers' best 10 at the end of a scan, a handful of
+        // survivors of a bounded scan): one warp sorts them in registers, no barrier, little code
         if (tid < 32) {
-            unsigned long long v = (tid < c) ? b.keys[tid] : 0ull;
-#pragma unroll
-            for (int size = 2; size <= 32; size <<= 1) {
-#pragma unroll
-                for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                    const unsigned long long o = shfl_xor_u64(v, stride);
-                    const bool lower = (tid & stride) == 0;
-                    const bool desc = (tid & size) == 0;
-                    v = ((v > o) == (lower == desc)) ? v : o;  // the lower lane of a descending pair keeps the larger key
-                }
-            }
-            const int keep = c < b.k ? c : b.k;
-            b.keys[tid] = (tid < keep) ? v : 0ull;
-            // the k-th key (lane k-1, when there are k) raises the threshold
-            const unsigned long long kth = shfl_u64(v, (b.k - 1) & 31);
-            if (tid == 0) {
-                b.ctrl->count = keep;
-                if (keep == b.k && kth > b.ctrl->thr) b.ctrl->thr = kth;  // only ever rises
-            }
+            if (c <= 32) warp_sort_prune<1>(b, c, tid);
+            else if (c <= 64) warp_sort_prune<2>(b, c, tid);
+            else warp_sort_prune<4>(b, c, tid);
         }
         __syncthreads();
         return;
