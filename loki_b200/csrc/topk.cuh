@@ -4,7 +4,7 @@
 // offers it to a per-CTA candidate buffer in shared memory.  A key is stored only
 // if it beats the CTA's current threshold (the k-th best key seen so far), so after
 // a short warm-up almost every row costs one compare.  When the buffer runs full
-// the CTA sorts it (bitonic, in shared memory), keeps the best k and raises the
+// the CTA sorts it (a bitonic network held in registers, see block_sort_desc), keeps the best k and raises the
 // threshold.  Scores therefore never travel to HBM: a CTA writes k keys at the end,
 // and the last CTA to finish merges all CTAs' lists with the same machinery.
 //
