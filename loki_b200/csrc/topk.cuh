@@ -147,11 +147,12 @@ __device__ __noinline__ inline void block_sort_desc(unsigned long long *keys, in
 // cand_prune for up to 32 R keys, by one warp: key i sits in register i / 32 of lane i % 32.  A bitonic
 // network: partners up to 16 apart meet through shuffles, partners 32 and 64 apart in the lane's own
 // registers.  Keeps the best k, zeroes the rest, raises the threshold.
+// Not inlined (like block_sort_desc): cand_prune sits in dozens of kernel instantiations.
 template <int R>
-__device__ __forceinline__ void warp_sort_prune(const CandBuf &b, int c, int lane) {
+__device__ __noinline__ void warp_sort_prune(unsigned long long *keys, CandCtrl *ctrl, int k, int c, int lane) {
     unsigned long long v[R];
 #pragma unroll
-    for (int e = 0; e < R; ++e) v[e] = (e * 32 + lane < c) ? b.keys[e * 32 + lane] : 0ull;
+    for (int e = 0; e < R; ++e) v[e] = (e * 32 + lane < c) ? keys[e * 32 + lane] : 0ull;
 #pragma unroll
     for (int size = 2; size <= 32 * R; size <<= 1) {
 #pragma unroll
@@ -179,17 +180,17 @@ __device__ __forceinline__ void warp_sort_prune(const CandBuf &b, int c, int lan
             }
         }
     }
-    const int keep = c < b.k ? c : b.k;
+    const int keep = c < k ? c : k;
     unsigned long long kth = 0ull;
 #pragma unroll
     for (int e = 0; e < R; ++e) {
-        b.keys[e * 32 + lane] = (e * 32 + lane < keep) ? v[e] : 0ull;
-        const unsigned long long at = shfl_u64(v[e], (b.k - 1) & 31);  // the k-th key, when there are k
-        if (((b.k - 1) >> 5) == e) kth = at;
+        keys[e * 32 + lane] = (e * 32 + lane < keep) ? v[e] : 0ull;
+        const unsigned long long at = shfl_u64(v[e], (k - 1) & 31);  // the k-th key, when there are k
+        if (((k - 1) >> 5) == e) kth = at;
     }
     if (lane == 0) {
-        b.ctrl->count = keep;
-        if (keep == b.k && kth > b.ctrl->thr) b.ctrl->thr = kth;  // only ever rises
+        ctrl->count = keep;
+        if (keep == k && kth > ctrl->thr) ctrl->thr = kth;  // only ever rises
     }
 }
 
@@ -202,9 +203,9 @@ __device__ inline void cand_prune(const CandBuf &b) {
         // few keys (a CTA's warps handing over their registers' best 10 at the end of a scan, a handful of
         // survivors of a bounded scan): one warp sorts them in registers, no barrier, little code
         if (tid < 32) {
-            if (c <= 32) warp_sort_prune<1>(b, c, tid);
-            else if (c <= 64) warp_sort_prune<2>(b, c, tid);
-            else warp_sort_prune<4>(b, c, tid);
+            if (c <= 32) warp_sort_prune<1>(b.keys, b.ctrl, b.k, c, tid);
+            else if (c <= 64) warp_sort_prune<2>(b.keys, b.ctrl, b.k, c, tid);
+            else warp_sort_prune<4>(b.keys, b.ctrl, b.k, c, tid);
         }
         __syncthreads();
         return;
